@@ -118,6 +118,23 @@ struct ClusterBarrierArrive {
     }
 };
 
+// The same remote arrive without release ordering: for hand-overs that publish no generic-proxy memory (a
+// tensor-memory stage whose reads have completed under tcgen05.wait::ld and fence::before_thread_sync).  The
+// releasing form orders all earlier memory operations of the thread at cluster scope first, which costs
+// several hundred nanoseconds per arrive.
+struct ClusterBarrierArriveRelaxed {
+    AXP_DEV static void execute(uint64_t* bar, uint32_t cta_rank) {
+        asm volatile(
+            "{\n\t"
+            ".reg .b32 remote;\n\t"
+            "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+            "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [remote];\n\t"
+            "}\n" ::"r"(smem_u32(bar)),
+            "r"(cta_rank)
+            : "memory");
+    }
+};
+
 // Non-blocking probe (the reference models it as BarrierTryWait writing a flag,
 // include/axp/realize/sm90.hpp:1300-1322).
 struct BarrierTryWait {
