@@ -10,8 +10,13 @@ torch.distributed.run, one rank per GPU) the output columns are sharded: every
 rank owns an 8192-column shard of a global N = 8192*N problem (weak scaling), A
 is replicated, there is no data-path collective.
 
-Other workloads (--workload): gemm_bf16_gate_up, gemm_bf16_down, gemm_bf16_swiglu, gemm_fp8_swiglu, attn_bf16, attn_fp8,
-quantize_fp8, rmsnorm_quantize_fp8, attn_decode_bf16, attn_decode_fp8.
+The default run also times, in the same process, the other workloads of the metric as sub-records under "workloads"
+(bf16 gate/up and down GEMMs, bf16 causal attention, FP8 GQA attention; with N > 1 the attention problems and one
+8192^3 FP8 GEMM are SPLIT over the ranks, and "gather" times the NCCL all-gather of the GEMM's column shards), a loop
+of at least two seconds ("sustained") and one library E4M3 GEMM as a reference point ("library_reference").
+
+Other workloads (--workload): gemm_fp8_strong, gemm_bf16_gate_up, gemm_bf16_down, gemm_bf16_swiglu, gemm_fp8_swiglu,
+attn_bf16, attn_fp8, quantize_fp8, rmsnorm_quantize_fp8, attn_decode_bf16, attn_decode_fp8.
 
 `--impl reference` times the CPU host oracle (the reference library has no
 runnable implementation of this path) on the box's host cores, on a bounded row
@@ -31,7 +36,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "FP8 GEMM & attn-fwd TFLOP/s per B200 (% of dense peak) at 1/2/4/8 GPUs"
-NOMINAL_TFLOPS = {"u8": 4500.0, "bf16": 2250.0}
+NOMINAL_TFLOPS = {"e4m3": 4500.0, "bf16": 2250.0}
+NVLINK_PEER_GBS = 770.0      # measured peer copy per direction on this pool (nominal 900)
+# workloads the default run adds beside the headline one, as sub-records under "workloads"
+EXTRA_WORKLOADS = ("gemm_bf16_gate_up", "gemm_bf16_down", "attn_bf16", "attn_fp8")
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of each workload's kernel, from the Nsight Compute
 # captures summarised in profiles/*.md (same shapes as the bench; not measured by this script)
 NCU_DRAM_BYTES_PER_LAUNCH = {
@@ -66,11 +74,17 @@ class Workload:
 
     name = ""
     dtype = ""
-    flops = 0.0          # algorithmic work per step: flops (tensor-bound workloads) or bytes (HBM-bound ones)
+    flops = 0.0          # algorithmic work per step of THIS rank: flops (tensor-bound workloads) or bytes (HBM-bound ones)
     bound = "tensor"
+    scaling = "weak"     # "weak": every rank runs the named shape; "strong": the named shape is split over the ranks
+    job_flops = None     # strong scaling: the work of the whole job per step (the named shape)
 
     def __init__(self, pkg, dev, rank, world):
         self.pkg, self.dev, self.rank, self.world = pkg, dev, rank, world
+
+    def total_work(self):
+        """Work of all ranks per step."""
+        return self.job_flops if self.scaling == "strong" else self.flops * self.world
 
     def step(self, i):  # device-resident pass
         raise NotImplementedError
@@ -81,8 +95,9 @@ class Workload:
 
 class GemmFp8(Workload):
     name = "cfg1: FP8 E4M3 block-scaled GEMM M=N=K=8192 per GPU (1x128 A scales, 128x128 B scales, bf16 out)"
-    dtype = "u8"
+    dtype = "e4m3"
     M = N = K = 8192
+    replicated_inputs = (0, 2)     # A and sA are the same on every rank (e2e: uploaded once, broadcast over NVLink)
 
     def __init__(self, pkg, dev, rank, world, sets=2):
         import torch
@@ -121,6 +136,44 @@ class GemmFp8(Workload):
         sa, sb = sA[:rows].cpu().numpy(), sB.cpu().numpy()
         out = np.zeros((rows, self.N), dtype=np.uint16)
         return (lambda: oracle.gemm_fp8_blockscaled(a, b, sa, sb, out=out)), 2.0 * rows * self.N * self.K
+
+
+class GemmFp8Strong(Workload):
+    """cfg1 as BASELINE.json words it for N GPUs: ONE 8192^3 problem whose output columns are split over the ranks
+    (boundaries at multiples of 256); A and sA replicated, no collective unless the full C is asked for."""
+    dtype = "e4m3"
+    scaling = "strong"
+    M = N = K = 8192
+
+    def __init__(self, pkg, dev, rank, world, sets=2):
+        import torch
+
+        super().__init__(pkg, dev, rank, world)
+        self.n0, self.n1 = pkg.shard.gemm_column_range(self.N, world, rank)
+        w = self.n1 - self.n0
+        self.name = f"cfg1 strong: ONE FP8 E4M3 block-scaled GEMM M=N=K=8192 split by output columns over {world} GPUs ({w} columns on this rank)"
+        self.job_flops = 2.0 * self.M * self.N * self.K
+        self.flops = 2.0 * self.M * w * self.K
+        self.bytes_min = self.M * self.K + w * self.K + 2 * self.M * w
+        self.sets = []
+        for s in range(sets):
+            A, B, sA, sB = pkg.synth.fp8_gemm_inputs(self.M, self.N, self.K, seed=s, device=dev)      # same seed on every rank
+            Bl, sBl = B[self.n0:self.n1].contiguous(), sB[self.n0 // 128:(self.n1 + 127) // 128].contiguous()
+            del B, sB
+            self.sets.append((A, Bl, sA, sBl, torch.empty((self.M, w), dtype=torch.bfloat16, device=dev)))
+
+    def step(self, i):
+        A, B, sA, sB, C = self.sets[i % len(self.sets)]
+        self.pkg.ops.gemm_fp8_blockscaled(A, B, sA, sB, out=C)        # the shard is a GEMM of its own: B rows = its columns
+
+    def e2e_spec(self):
+        import torch
+
+        A, B, sA, sB, C = self.sets[0]
+        dev_in = [A.view(torch.uint8), B.view(torch.uint8), sA, sB]
+        return (lambda i, o: self.pkg.ops.gemm_fp8_blockscaled(i[0], i[1], i[2], i[3], out=o[0])), dev_in, [C]
+
+    replicated_inputs = (0, 2)
 
 
 class GemmBf16(Workload):
@@ -200,7 +253,7 @@ class GemmBf16SwiGLU(Workload):
 
 class GemmFp8SwiGLU(Workload):
     """The same gate / up pass on E4M3 block-scaled operands (1x128 activation scales, 128x128 weight scales)."""
-    dtype = "u8"
+    dtype = "e4m3"
     M, N, K = 16384, 14336, 4096
 
     def __init__(self, pkg, dev, rank, world, sets=2):
@@ -244,16 +297,23 @@ class AttnBf16(Workload):
         import torch
 
         super().__init__(pkg, dev, rank, world)
-        self.flops = 0.5 * 4.0 * self.B * self.H * self.S * self.S * self.D
-        self.bytes_min = 4 * 2 * self.B * self.H * self.S * self.D + 4 * self.B * self.H * self.S
+        # N GPUs: the 256 (batch, head) units of the ONE named problem are split into contiguous ranges, no collective
+        self.bh = pkg.shard.attention_head_range(self.B, self.H, self.H, world, rank)
+        heads = self.bh[1] - self.bh[0]
+        self.job_flops = 0.5 * 4.0 * self.B * self.H * self.S * self.S * self.D
+        self.flops = self.job_flops * heads / (self.B * self.H)
+        self.bytes_min = (4 * 2 * self.S * self.D + 4 * self.S) * heads
+        if world > 1:
+            self.scaling = "strong"
+            self.name += f" -- split by batch x head over {world} GPUs ({heads} heads on this rank)"
         self.sets = []
         for s in range(sets):
-            Q, K, V, self.scale = pkg.synth.bf16_attention_inputs(self.B, self.H, self.S, self.D, seed=100 * rank + s, device=dev)
+            Q, K, V, self.scale = pkg.synth.bf16_attention_inputs(self.B, self.H, self.S, self.D, seed=s, device=dev)
             self.sets.append((Q, K, V, torch.empty_like(Q), torch.empty((self.B, self.H, self.S), dtype=torch.float32, device=dev)))
 
     def step(self, i):
         Q, K, V, O, L = self.sets[i % len(self.sets)]
-        self.pkg.ops.attn_fwd_bf16(Q, K, V, self.scale, True, out=O, lse=L)
+        self.pkg.ops.attn_fwd_bf16(Q, K, V, self.scale, True, out=O, lse=L, bh_range=self.bh)
 
     def e2e_spec(self):
         Q, K, V, O, L = self.sets[0]
@@ -273,26 +333,33 @@ class AttnBf16(Workload):
 
 class AttnFp8(Workload):
     name = "cfg4: FP8 attention fwd GQA causal B=4 Hq=64 Hkv=8 S=8192 D=128 per GPU (causal flops)"
-    dtype = "u8"
+    dtype = "e4m3"
     B, Hq, Hkv, S, D = 4, 64, 8, 8192, 128
 
     def __init__(self, pkg, dev, rank, world, sets=2):
         import torch
 
         super().__init__(pkg, dev, rank, world)
-        self.flops = 0.5 * 4.0 * self.B * self.Hq * self.S * self.S * self.D
-        self.bytes_min = self.B * self.S * self.D * (self.Hq + 2 * self.Hkv + 2 * self.Hq)
+        # N GPUs: the 32 (batch, KV-head group) units of the ONE named problem are split, whole groups per rank
+        self.bh = pkg.shard.attention_head_range(self.B, self.Hq, self.Hkv, world, rank)
+        heads = self.bh[1] - self.bh[0]
+        self.job_flops = 0.5 * 4.0 * self.B * self.Hq * self.S * self.S * self.D
+        self.flops = self.job_flops * heads / (self.B * self.Hq)
+        self.bytes_min = self.S * self.D * (3 * heads + 2 * heads * self.Hkv // self.Hq)
+        if world > 1:
+            self.scaling = "strong"
+            self.name += f" -- split by batch x KV-head group over {world} GPUs ({heads} query heads on this rank)"
         self.sets = []
         for s in range(sets):
             Q, K, V, dq, dk, dv, self.scale = pkg.synth.fp8_attention_inputs(self.B, self.Hq, self.Hkv, self.S, self.D,
-                                                                             seed=100 * rank + s, device=dev)
+                                                                             seed=s, device=dev)
             O = torch.empty((self.B, self.Hq, self.S, self.D), dtype=torch.bfloat16, device=dev)
             L = torch.empty((self.B, self.Hq, self.S), dtype=torch.float32, device=dev)
             self.sets.append((Q, K, V, dq, dk, dv, O, L))
 
     def step(self, i):
         Q, K, V, dq, dk, dv, O, L = self.sets[i % len(self.sets)]
-        self.pkg.ops.attn_fwd_fp8(Q, K, V, dq, dk, dv, self.scale, True, out=O, lse=L)
+        self.pkg.ops.attn_fwd_fp8(Q, K, V, dq, dk, dv, self.scale, True, out=O, lse=L, bh_range=self.bh)
 
     def e2e_spec(self):
         import torch
@@ -432,7 +499,7 @@ class AttnDecodeFp8(Workload):
     pass over their K / V."""
     name = "decode: E4M3 attention, 1 query per head, B=16 Hq=32 Hkv=8 Skv=16384 D=128 per GPU, split-KV x2 (KV cache read once)"
     metric = "decode attention: KV-cache GB/s per B200 (algorithmic bytes = K and V read once)"
-    dtype = "u8"
+    dtype = "e4m3"
     bound = "hbm"
     launches_per_step = 2      # the pass over the KV shares and the combine kernel
     B, Hq, Hkv, Sq, Skv, D, SPLITS = 16, 32, 8, 1, 16384, 128, 2
@@ -476,6 +543,8 @@ class AttnDecodeFp8(Workload):
 def make_workload(name, pkg, dev, rank, world):
     if name == "gemm_fp8":
         return GemmFp8(pkg, dev, rank, world)
+    if name == "gemm_fp8_strong":
+        return GemmFp8Strong(pkg, dev, rank, world)
     if name == "gemm_bf16_gate_up":
         return GemmBf16(pkg, dev, rank, world, 16384, 14336, 4096, "gate/up")
     if name == "gemm_bf16_down":
@@ -562,6 +631,7 @@ def time_cpu(fn, budget_s):
 def cpu_baseline(wl, budget_s=12.0):
     from oracle import host_oracle
 
+    host_oracle.set_num_threads(host_threads())
     rows = 64
     fn, fl = wl.cpu_sample(host_oracle, rows)
     t = time_cpu(fn, 0.5)
@@ -576,6 +646,23 @@ def cpu_baseline(wl, budget_s=12.0):
             "sample": f"host oracle on a {target_rows}-row-equivalent slice of the workload ({fl:.3e} {'bytes' if hbm else 'flop'} per call, {t:.2f} s per call)"}
 
 
+def config_for(wl, world):
+    """The `config` object both arms print (identical keys and wording)."""
+    return {"workload": wl.name,
+            "sharding": ("single GPU" if world == 1 else
+                         "headline workload: every rank runs the named shape on its own output-column shard of a world-times wider problem "
+                         "(weak scaling, no data-path collective); attention sub-records split the ONE named problem by heads (strong)"),
+            "l2": "two operand sets alternate between steps; each set (>= 130 MB per rank) exceeds the 126 MB L2",
+            "timing": "GPU arm: CUDA events on the launch stream, max over ranks; reference arm: host wall clock of the CPU oracle"}
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def run_reference(args, rank):
     """Reference arm: the CPU host oracle with all host threads, bounded sample per step."""
     if rank != 0:
@@ -585,6 +672,8 @@ def run_reference(args, rank):
     pkg = importlib.import_module("iro-cuda-ax_b200")
     from oracle import host_oracle
 
+    # launchers such as torch.distributed.run export OMP_NUM_THREADS=1: ask for every host core explicitly
+    host_oracle.set_num_threads(host_threads())
     dev = torch.device("cpu")
     wl = make_workload(args.workload, pkg, dev, 0, 1) if args.workload != "gemm_fp8" else GemmFp8(pkg, dev, 0, 1, sets=1)
     fn, fl = wl.cpu_sample(host_oracle, 64)
@@ -599,30 +688,226 @@ def run_reference(args, rank):
     for _ in range(args.steps):
         fn()
     el = time.perf_counter() - t0
-    val = fl * args.steps / el / 1e12
-    sample = f"{rows}-row-equivalent slice of the workload per step ({fl:.3e} flop), OpenMP over all host threads"
+    hbm = wl.bound == "hbm"
+    unit = "GB/s" if hbm else "TFLOP/s"
+    val = fl * args.steps / el / (1e9 if hbm else 1e12)
+    sample = (f"{rows}-row-equivalent slice of the workload per step ({fl:.3e} {'bytes' if hbm else 'flop'}), OpenMP over "
+              f"{host_oracle.num_threads()} host threads; the reference library has no runnable implementation of this path, "
+              "this arm times the CPU host oracle (a port of the recipe semantics)")
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": getattr(wl, "metric", METRIC), "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": {"workload": wl.name, "note": "the reference library has no runnable implementation of this path; "
-                   "this arm times the CPU host oracle (a port of the recipe semantics)"},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": host_oracle.num_threads(), "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": config_for(wl, max(1, args.gpus)),
+        "cpu_baseline": {"value": val, "unit": unit, "cores": host_oracle.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+# ------------------------------------------------------------ GPU measurement ----
+class Ctx:
+    """What the measurement helpers share: device, ranks, the package, peaks."""
+
+    def __init__(self, pkg, dev, rank, local_rank, world, dist, peaks):
+        self.pkg, self.dev, self.rank, self.local_rank, self.world, self.dist, self.peaks = pkg, dev, rank, local_rank, world, dist, peaks
+
+    def barrier(self):
+        import torch
+
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, x):
+        import torch
+
+        t = torch.tensor([x], dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+def measure(ctx, wl, steps, warmup):
+    """W untimed steps, then K steps between a barrier + synchronize on both sides, CUDA events on the launch stream
+    (one per launch as well), clocks sampled during the timed region; time = max over ranks."""
+    import torch
+
+    for i in range(warmup):
+        wl.step(i)
+    ctx.pkg.ops.check_status(ctx.dev)
+    ctx.barrier()
+    sampler = ClockSampler(ctx.local_rank)
+    sampler.start()
+    stream = torch.cuda.current_stream()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record(stream)
+    for i in range(steps):
+        wl.step(i)
+        evs[i + 1].record(stream)
+    ctx.barrier()
+    sampler.stop_flag = True
+    sampler.join()
+    ctx.pkg.ops.check_status(ctx.dev)
+    per_launch = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(steps))
+    total_ms = ctx.max_over_ranks(evs[0].elapsed_time(evs[-1]))
+    return {"ms_per_step": total_ms / steps, "kernel_ms": sum(per_launch) / len(per_launch), "kernel_ms_min": per_launch[0],
+            "clocks": sampler.result(), "timed_s": total_ms * 1e-3}
+
+
+def roofline(ctx, wl, key, m):
+    """achieved = this rank's algorithmic work per launch / mean launch time; the tensor peak is the cuBLAS bf16 figure of
+    MEASURED_PEAKS.json that matches the length of the timed region: the burst figure under one second, else the sustained one."""
+    peaks = ctx.peaks
+    hbm = wl.bound == "hbm"
+    per = 1e9 if hbm else 1e12
+    achieved = wl.flops / (m["kernel_ms"] * 1e-3) / per
+    traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(key) if wl.scaling == "weak" or ctx.world == 1 else None
+    loud = "" if peaks["source"] == "measured" else "FALLBACK (MEASURED_PEAKS.json is missing): "
+    if hbm:
+        peak = peaks["hbm_gbs"]
+        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+                "peak_source": f"{loud}{peaks['source']} STREAM-style copy {peak} GB/s", "kernel_ms": m["kernel_ms"],
+                "kernel_ms_min": m["kernel_ms_min"], "hbm_min_bytes": wl.bytes_min}
+    burst = m["timed_s"] < 1.0
+    bf16_peak = peaks["bf16_burst"] if burst else peaks["bf16_sustained"]
+    eight_bit = wl.dtype == "e4m3"
+    peak = bf16_peak * (2.0 if eight_bit else 1.0)
+    return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
+            "peak_kind": "burst" if burst else "sustained",
+            "peak_source": (f"{loud}{peaks['source']} cuBLAS bf16 {'burst' if burst else 'sustained'} {bf16_peak} TFLOP/s "
+                            f"(timed region {m['timed_s'] * 1e3:.1f} ms {'<' if burst else '>='} 1 s)"
+                            + (", x2 for the 8-bit tensor rate: no E4M3 figure is measured there" if eight_bit else "")),
+            "frac_of_nominal": achieved / NOMINAL_TFLOPS[wl.dtype], "nominal_peak": NOMINAL_TFLOPS[wl.dtype],
+            "kernel_ms": m["kernel_ms"], "kernel_ms_min": m["kernel_ms_min"], "hbm_min_bytes": wl.bytes_min,
+            "hbm_gbs_at_min_bytes": wl.bytes_min / (m["kernel_ms"] * 1e-3) / 1e9}
+
+
+def sub_record(ctx, wl, key, steps, warmup):
+    m = measure(ctx, wl, steps, warmup)
+    hbm = wl.bound == "hbm"
+    per = 1e9 if hbm else 1e12
+    rec = {"workload": wl.name, "value": wl.total_work() / (m["ms_per_step"] * 1e-3) / per, "unit": "GB/s" if hbm else "TFLOP/s",
+           "scaling": wl.scaling if ctx.world > 1 else "single GPU", "dtype": wl.dtype, "steps": steps, "ms_per_step": m["ms_per_step"],
+           "kernel_ms": m["kernel_ms"], "clocks": m["clocks"], "gpu_launches": steps * getattr(wl, "launches_per_step", 1)}
+    if ctx.rank == 0:
+        rec["roofline"] = roofline(ctx, wl, key, m)
+    return rec, m
+
+
+def sustained_record(ctx, wl, ms_per_step, seconds=2.0):
+    """The same launches back to back for at least `seconds`: what the power cap leaves once the burst is over."""
+    steps = max(50, int(seconds * 1e3 / max(ms_per_step, 1e-3)) + 1)
+    m = measure(ctx, wl, steps, 0)
+    val = wl.total_work() / (m["ms_per_step"] * 1e-3) / 1e12
+    per_gpu = wl.flops / (m["kernel_ms"] * 1e-3) / 1e12
+    peak = ctx.peaks["bf16_sustained"] * (2.0 if wl.dtype == "e4m3" else 1.0)
+    return {"value": val, "unit": "TFLOP/s", "steps": steps, "seconds": m["timed_s"], "ms_per_step": m["ms_per_step"], "clocks": m["clocks"],
+            "frac_of_sustained_peak": per_gpu / peak, "sustained_peak": peak, "frac_of_nominal": per_gpu / NOMINAL_TFLOPS[wl.dtype],
+            "note": "time x median SM MHz lets a reader normalise between runs; no clock setting is touched"}
+
+
+def library_reference(ctx, steps=20):
+    """One library E4M3 GEMM (torch._scaled_mm = cuBLASLt, per-tensor scales, 8192^3, bf16 out) timed in this process as a stated
+    reference point for what the tensor pipe of this box delivers in E4M3.  Never on the product path."""
+    import torch
+
+    try:
+        M = N = K = 8192
+        a = torch.randn((M, K), device=ctx.dev).to(torch.float8_e4m3fn)
+        b = torch.randn((N, K), device=ctx.dev).to(torch.float8_e4m3fn)
+        one = torch.ones((), device=ctx.dev, dtype=torch.float32)
+        fn = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"what": "torch._scaled_mm (cuBLASLt) E4M3 x E4M3 -> bf16, per-tensor scales, M=N=K=8192 (no block scales: not the same recipe)",
+                "value": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps}
+    except Exception as e:  # the library call is a reference point only
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+
+def e2e_record(ctx, wl, n_steps):
+    """The same metric through the host-buffer entry: pinned host operands in, host result out, every step.  With several
+    ranks, operands that are replicated on every rank (`wl.replicated_inputs`) are uploaded by rank 0 only and reach the others by
+    an NCCL broadcast over NVLink."""
+    import torch
+
+    hostpipe = importlib.import_module("iro-cuda-ax_b200.hostpipe")
+    launch, dev_in, dev_out = wl.e2e_spec()
+    rep = set(getattr(wl, "replicated_inputs", ())) if ctx.world > 1 else set()
+    host_in = [None if (i in rep and ctx.rank != 0) else t.cpu().pin_memory() for i, t in enumerate(dev_in)]
+    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in dev_out]
+    h2d = sum(t.numel() * t.element_size() for t in host_in if t is not None)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+    bcast = sum(dev_in[i].numel() * dev_in[i].element_size() for i in rep)
+    pipe = hostpipe.HostPipeline(launch, dev_in, dev_out, broadcast=(sorted(rep), ctx.dist) if rep else None)
+    for _ in range(3):
+        pipe.submit(host_in, host_out)
+    pipe.drain()
+    ctx.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(pipe.s_in)
+    for _ in range(n_steps):
+        pipe.submit(host_in, host_out)
+    pipe.record_done(e1)
+    pipe.drain()
+    ctx.barrier()
+    ctx.pkg.ops.check_status(ctx.dev)
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / n_steps
+    hbm = wl.bound == "hbm"
+    tot = torch.tensor([float(h2d), float(d2h)], dtype=torch.float64, device=ctx.dev)
+    if ctx.world > 1:
+        ctx.dist.all_reduce(tot)
+    return {"value": wl.total_work() / (ms * 1e-3) / (1e9 if hbm else 1e12), "unit": "GB/s" if hbm else "TFLOP/s",
+            "h2d_bytes_per_step": int(tot[0].item()), "d2h_bytes_per_step": int(tot[1].item()), "ms_per_step": ms, "steps": n_steps,
+            "host_link_gbs": (tot[0].item() + tot[1].item()) / (ms * 1e-3) / 1e9,
+            "nvlink_broadcast_bytes_per_step": bcast,
+            "path": "hostpipe.HostPipeline: pinned host operands -> H2D -> C-ABI kernel -> D2H of the result, every step; three streams, "
+                    "two buffer slots; byte counts are summed over all ranks"
+                    + ("; replicated operands are uploaded once (rank 0) and broadcast over NVLink (NCCL)" if rep else "")}
+
+
+def gather_record(ctx, wl, steps):
+    """N-sharded GEMM with the full C requested: NCCL all-gather of the column shards + strided placement, timed alone."""
+    import torch
+
+    C = wl.sets[0][4]
+    full = torch.empty((wl.M, wl.N), dtype=torch.bfloat16, device=ctx.dev)
+    for _ in range(3):
+        ctx.pkg.shard.all_gather_columns(C, wl.N, ctx.world, out=full)
+    ctx.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        ctx.pkg.shard.all_gather_columns(C, wl.N, ctx.world, out=full)
+    e1.record()
+    ctx.barrier()
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / steps
+    recv = 2.0 * wl.M * wl.N * (ctx.world - 1) / ctx.world
+    return {"ms": ms, "bytes_received_per_gpu": int(recv), "gbs_per_gpu": recv / (ms * 1e-3) / 1e9,
+            "frac_of_nvlink_peer_copy": recv / (ms * 1e-3) / 1e9 / NVLINK_PEER_GBS, "nvlink_reference_gbs": NVLINK_PEER_GBS,
+            "what": "shard.all_gather_columns: one NCCL all-gather of the row-major [M, w] bf16 shards + one strided placement pass per rank"}
 
 
 # ----------------------------------------------------------------------- main ----
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="gemm_fp8",
-                    choices=["gemm_fp8", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8"])
+                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="headline workload only: no sub-records, no sustained loop, no library reference")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -647,107 +932,56 @@ def main():
 
     pkg = importlib.import_module("iro-cuda-ax_b200")
     pkg.capi.lib()                                 # fail loudly if the CUDA library is missing
+    ctx = Ctx(pkg, dev, rank, local_rank, world, dist, load_peaks())
     wl = make_workload(args.workload, pkg, dev, rank, world)
-    peaks = load_peaks()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing -------------------------------------------------
-    for i in range(args.warmup):
-        wl.step(i)
-    pkg.ops.check_status(dev)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    stream = torch.cuda.current_stream()
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    evs[0].record(stream)
-    for i in range(args.steps):
-        wl.step(i)
-        evs[i + 1].record(stream)
-    barrier()
-    sampler.stop_flag = True
-    sampler.join()
-    pkg.ops.check_status(dev)
-    total_ms = evs[0].elapsed_time(evs[-1])
-    per_launch_ms = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps))
-    kernel_ms = sum(per_launch_ms) / len(per_launch_ms)
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
     hbm = wl.bound == "hbm"
     unit = "GB/s" if hbm else "TFLOP/s"
     per = 1e9 if hbm else 1e12
-    metric = getattr(wl, "metric", METRIC)
-    value = wl.flops * world / (ms_per_step * 1e-3) / per
 
-    # ---- end to end: host buffers in, host result out, every step ----------------
-    e2e = None
-    if not args.no_e2e:
-        hostpipe = importlib.import_module("iro-cuda-ax_b200.hostpipe")
-        launch, dev_in, dev_out = wl.e2e_spec()
-        host_in = [t.cpu().pin_memory() for t in dev_in]
-        host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in dev_out]
-        h2d = sum(t.numel() * t.element_size() for t in host_in)
-        d2h = sum(t.numel() * t.element_size() for t in host_out)
-        pipe = hostpipe.HostPipeline(launch, dev_in, dev_out)
-        n_e2e = max(4, min(args.steps, 24))
-        for _ in range(3):
-            pipe.submit(host_in, host_out)
-        pipe.drain()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(pipe.s_in)
-        for _ in range(n_e2e):
-            pipe.submit(host_in, host_out)
-        pipe.record_done(e1)
-        pipe.drain()
-        barrier()
-        pkg.ops.check_status(dev)
-        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item()) / n_e2e
-        e2e = {"value": wl.flops * world / (e2e_ms * 1e-3) / per, "unit": unit, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e,
-               "path": "hostpipe.HostPipeline: pinned host operands -> H2D -> C-ABI kernel -> D2H of the result, every step; "
-                       "three streams, two buffer slots"}
-
+    # ---- headline workload: device-resident timing --------------------------------
+    m = measure(ctx, wl, args.steps, args.warmup)
+    value = wl.total_work() / (m["ms_per_step"] * 1e-3) / per
+    line = {
+        "metric": getattr(wl, "metric", METRIC), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": m["ms_per_step"], "higher_is_better": True,
+        "scaling": wl.scaling if world > 1 else "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": config_for(wl, world), "clocks": m["clocks"], "e2e": None,
+        "gpu_launches": args.steps * getattr(wl, "launches_per_step", 1),
+    }
     if rank == 0:
-        bf16_peak = peaks["bf16_sustained"]
-        achieved = wl.flops / (kernel_ms * 1e-3) / per
-        traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
-        if hbm:
-            peak = peaks["hbm_gbs"]
-            roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-                    "peak_source": f"{peaks['source']} STREAM-style copy {peak} GB/s", "kernel_ms": kernel_ms,
-                    "kernel_ms_min": per_launch_ms[0], "hbm_min_bytes": wl.bytes_min}
-        else:
-            peak = bf16_peak * (2.0 if wl.dtype == "u8" else 1.0)
-            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": traffic,
-                    "peak_source": (f"{peaks['source']} cuBLAS bf16 sustained {bf16_peak} TFLOP/s"
-                                    + (" x2 for the 8-bit tensor rate" if wl.dtype == "u8" else "")),
-                    "frac_of_nominal": achieved / NOMINAL_TFLOPS[wl.dtype], "nominal_peak": NOMINAL_TFLOPS[wl.dtype],
-                    "kernel_ms": kernel_ms, "kernel_ms_min": per_launch_ms[0], "hbm_min_bytes": wl.bytes_min,
-                    "hbm_gbs_at_min_bytes": wl.bytes_min / (kernel_ms * 1e-3) / 1e9}
-        line = {
-            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": {"workload": wl.name, "sharding": "output columns / heads / rows per rank, no collective" if world > 1 else "single GPU",
-                       "l2": "two operand sets alternate between steps; each set (>= 270 MB) exceeds the 126 MB L2",
-                       "timing": "CUDA events on the launch stream, max over ranks"},
-            "clocks": sampler.result(),
-            "e2e": e2e,
-            "gpu_launches": args.steps * getattr(wl, "launches_per_step", 1),
-            "roofline": roof,
-        }
+        line["roofline"] = roofline(ctx, wl, args.workload, m)
+    extras = args.workload == "gemm_fp8" and not args.no_extra
+
+    # ---- end to end: host buffers in, host result out, every step ------------------
+    if not args.no_e2e:
+        line["e2e"] = e2e_record(ctx, wl, max(4, min(args.steps, 24)))
+
+    # ---- the other workloads of the metric, same process (sub-records) -------------
+    if extras:
+        del wl
+        torch.cuda.empty_cache()
+        steps = max(5, min(args.steps, 20))
+        subs = {}
+        names = list(EXTRA_WORKLOADS) + (["gemm_fp8_strong"] if world > 1 else [])
+        for name in names:
+            w = make_workload(name, pkg, dev, rank, world)
+            torch.cuda.synchronize()
+            time.sleep(1.5)      # idle gap: the 20-step burst figure of one workload should not inherit the power state the previous one left
+            subs[name], _ = sub_record(ctx, w, name, steps, 3)
+            if name == "gemm_fp8_strong":
+                g = gather_record(ctx, w, steps)
+                g["gemm_ms"] = subs[name]["ms_per_step"]
+                g["gemm_plus_gather_ms"] = subs[name]["ms_per_step"] + g["ms"]
+                line["gather"] = g
+            del w
+            torch.cuda.empty_cache()
+        line["workloads"] = subs
+        if rank == 0:
+            line["library_reference"] = library_reference(ctx)
+        # last on the GPU, so that the burst figures above are not taken on a part the long loop has just driven into its power cap
+        wl = make_workload(args.workload, pkg, dev, rank, world)
+        line["sustained"] = sustained_record(ctx, wl, m["ms_per_step"])
+    if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(line))

@@ -68,7 +68,9 @@ uint64_t axp_sm100_fnv1a64(const char* s);
  * layout of the reference recipe (include/axp/level3/gemm.hpp:1162-1176); fp32
  * accumulate with one partial per K tile (gemm.hpp:1512-1515); sA [M,K/128] and
  * sB [ceil(N/128),K/128] row-major fp32; C [M,N] bf16 (ldc).  Only output columns
- * [n_begin,n_end) are computed (N-sharding); n_begin must be a multiple of 128.
+ * [n_begin,n_end) are computed (N-sharding); n_begin must be a multiple of 128 and
+ * n_end - n_begin a multiple of 8 (every GEMM entry point of this header writes,
+ * and reads bias / C input, eight columns at a time; AXP_ERR_BAD_ARG otherwise).
  * Requires K % 128 == 0, lda/ldb % 16 == 0, ldc % 8 == 0, 16-byte aligned bases.
  * Realizes: GemmTilePattern on cap::sm100 (gemm.hpp:2276-2375 dispatch; the
  * ScaleSharedTile hook gemm.hpp:104-116,1379-1382 becomes a scale-and-promote of

@@ -788,6 +788,9 @@ int launch_gemm(const void* A, const void* B, const float* sA, const float* sB, 
         if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || n_begin % 8 != 0)
             return fail(AXP_ERR_BAD_ARG, "gemm bf16: K, lda, ldb and n_begin must be multiples of 8 elements");
     }
+    // the epilogues write (and read bias / C input) eight columns at a time
+    if ((n_end - n_begin) % 8 != 0)
+        return fail(AXP_ERR_BAD_ARG, "gemm: the column range [%lld,%lld) must span a multiple of 8 columns", (long long)n_begin, (long long)n_end);
     if (lda < K || ldb < K || ldc < N) return fail(AXP_ERR_BAD_ARG, "gemm: leading dimension smaller than the row length");
     if (ldc % 8 != 0) return fail(AXP_ERR_BAD_ARG, "gemm: ldc must be a multiple of 8 elements");
     if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return fail(AXP_ERR_BAD_ARG, "gemm: base pointers must be 16-byte aligned");
@@ -914,6 +917,8 @@ int launch_gated(const void* X, const void* Wg, const void* Wu, void* H, int64_t
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail(AXP_ERR_UNSUPPORTED, "gemm swiglu: extent above 2^31-1");
     if (K % 8 != 0 || ldx % 8 != 0 || ldwg % 8 != 0 || ldwu % 8 != 0 || ldh % 8 != 0 || n_begin % 8 != 0)
         return fail(AXP_ERR_BAD_ARG, "gemm swiglu: K, leading dimensions and n_begin must be multiples of 8 elements");
+    if ((n_end - n_begin) % 8 != 0)
+        return fail(AXP_ERR_BAD_ARG, "gemm swiglu: the column range [%lld,%lld) must span a multiple of 8 columns", (long long)n_begin, (long long)n_end);
     if (ldx < K || ldwg < K || ldwu < K || ldh < N) return fail(AXP_ERR_BAD_ARG, "gemm swiglu: leading dimension smaller than the row length");
     if (!aligned16(X) || !aligned16(Wg) || !aligned16(Wu) || !aligned16(H)) return fail(AXP_ERR_BAD_ARG, "gemm swiglu: base pointers must be 16-byte aligned");
     if (n_begin == n_end) return AXP_OK;
@@ -989,6 +994,8 @@ int launch_gated_fp8(const void* X, const void* Wg, const void* Wu, const float*
     if (n_begin % 128 != 0) return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu: n_begin=%lld is not a multiple of 128", (long long)n_begin);
     if (ldx % 16 != 0 || ldwg % 16 != 0 || ldwu % 16 != 0 || ldh % 8 != 0)
         return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu: operand leading dimensions must be multiples of 16, ldh of 8 elements");
+    if ((n_end - n_begin) % 8 != 0)
+        return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu: the column range [%lld,%lld) must span a multiple of 8 columns", (long long)n_begin, (long long)n_end);
     if (ldx < K || ldwg < K || ldwu < K || ldh < N) return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu: leading dimension smaller than the row length");
     if (!aligned16(X) || !aligned16(Wg) || !aligned16(Wu) || !aligned16(H)) return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu: base pointers must be 16-byte aligned");
     if (n_begin == n_end) return AXP_OK;

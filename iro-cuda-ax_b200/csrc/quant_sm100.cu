@@ -17,6 +17,11 @@ namespace rz = axp::realize::sm100;
 
 namespace {
 
+// Smallest block scale: the smallest normal float, so that 1 / scale stays finite (a block of denormal-sized values
+// would otherwise give inv = inf and turn its exact zeros into NaN codes).
+constexpr float kMinScale = 1.17549435e-38f;
+
+
 constexpr int kQuantThreads = 256;
 
 // A warp handles a chunk of 8 consecutive blocks (1024 elements) of one row per step: four 16-byte loads per
@@ -58,7 +63,7 @@ quantize_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restri
                 for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
 #pragma unroll
                 for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, 16));
-                const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+                const float scale = amax > 0.0f ? fmaxf(__fdiv_rn(amax, 448.0f), kMinScale) : 1.0f;
                 const float inv = __fdiv_rn(1.0f, scale);
                 if (kb < k_blocks) {
                     uint2 out;
@@ -143,7 +148,7 @@ rmsnorm_quantize_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, const __n
         for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
 #pragma unroll
         for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, 16));
-        const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+        const float scale = amax > 0.0f ? fmaxf(__fdiv_rn(amax, 448.0f), kMinScale) : 1.0f;
         const float inv = __fdiv_rn(1.0f, scale);
         if (live) {
             uint2 out;

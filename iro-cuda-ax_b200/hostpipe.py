@@ -17,8 +17,13 @@ class HostPipeline:
     ``inputs`` / ``outputs`` are example tensors (shape and dtype are taken from them;
     their device is the device to run on)."""
 
-    def __init__(self, launch, inputs, outputs, slots: int = 2):
+    def __init__(self, launch, inputs, outputs, slots: int = 2, broadcast=None):
+        """``broadcast`` = (input indices, torch.distributed module) for operands that are identical on every rank: rank 0
+        uploads them from its host buffer and an NCCL broadcast over NVLink delivers them to the other ranks, whose
+        ``host_inputs`` entries for these indices are ``None`` (one PCIe upload per job instead of one per rank)."""
         self.launch = launch
+        self.bcast_idx = set(broadcast[0]) if broadcast else set()
+        self.dist = broadcast[1] if broadcast else None
         self.device = inputs[0].device
         self.slots = slots
         self.dev_in = [[torch.empty_like(t) for t in inputs] for _ in range(slots)]
@@ -39,8 +44,11 @@ class HostPipeline:
         with torch.cuda.stream(self.s_in):
             if not first_use:
                 self.s_in.wait_event(self.ev_run[k])       # the kernel that read this slot's inputs is done
-            for d, h in zip(self.dev_in[k], host_inputs):
-                d.copy_(h, non_blocking=True)
+            for i, (d, h) in enumerate(zip(self.dev_in[k], host_inputs)):
+                if h is not None:
+                    d.copy_(h, non_blocking=True)
+                if i in self.bcast_idx:
+                    self.dist.broadcast(d, src=0)      # enqueued behind the upload on this stream
             self.ev_in[k].record(self.s_in)
         with torch.cuda.stream(self.s_run):
             self.s_run.wait_event(self.ev_in[k])

@@ -34,24 +34,29 @@ def attention_head_range(B: int, Hq: int, Hkv: int, world: int, rank: int) -> tu
     return shard_range(B * Hq, group, world, rank)
 
 
-def all_gather_columns(c_local, N: int, world: int, group=None):
+def all_gather_columns(c_local, N: int, world: int, group=None, out=None):
     """Full C [M,N] from the ranks' column shards (only when the caller wants the full output).
 
-    Every rank passes its [M, n1-n0] shard; shards may differ in width by one block."""
+    Every rank passes its row-major [M, n1-n0] shard.  One all-gather of the shards as they lie (bytes; a shard narrower
+    than the widest one is padded first), then one strided placement pass per rank into ``out`` [M,N] (allocated when
+    not given)."""
     import torch
     import torch.distributed as dist
 
     M = c_local.shape[0]
-    widths = [gemm_column_range(N, world, r) for r in range(world)]
-    wmax = max(e - b for b, e in widths)
-    pad = torch.zeros((wmax, M), dtype=c_local.dtype, device=c_local.device)
-    pad[: c_local.shape[1]] = c_local.t()
-    gathered = torch.empty((world * wmax, M), dtype=c_local.dtype, device=c_local.device)
+    ranges = [gemm_column_range(N, world, r) for r in range(world)]
+    wmax = max(e - b for b, e in ranges)
+    if c_local.shape[1] == wmax and c_local.is_contiguous():
+        send = c_local
+    else:
+        send = torch.zeros((M, wmax), dtype=c_local.dtype, device=c_local.device)
+        send[:, : c_local.shape[1]] = c_local
+    gathered = torch.empty((world * M, wmax), dtype=c_local.dtype, device=c_local.device)      # rank r's shard = rows [r M, (r+1) M)
     # bit patterns travel as bytes: every backend moves uint8, not every one moves bf16
-    dist.all_gather_into_tensor(gathered.view(torch.uint8), pad.view(torch.uint8), group=group)
-    full = torch.empty((M, N), dtype=c_local.dtype, device=c_local.device)
-    for r, (b, e) in enumerate(widths):
-        full[:, b:e] = gathered[r * wmax : r * wmax + (e - b)].t()
+    dist.all_gather_into_tensor(gathered.view(torch.uint8), send.view(torch.uint8), group=group)
+    full = out if out is not None else torch.empty((M, N), dtype=c_local.dtype, device=c_local.device)
+    for r, (b, e) in enumerate(ranges):
+        full[:, b:e].copy_(gathered[r * M : (r + 1) * M, : e - b])
     return full
 
 
@@ -80,8 +85,23 @@ def attn_kv_sharded(Q, K_local, V_local, scale: float, causal: bool, skv_total: 
     k0, k1 = kv_shard_range(skv_total, world, rank)
     if K_local.shape[2] != k1 - k0:
         raise ValueError(f"rank {rank} must hold keys [{k0},{k1}) of {skv_total}, got {K_local.shape[2]}")
-    part = partial_fn(Q, K_local, V_local, scale, causal, k0, skv_total)
+    if k1 > k0:
+        part = partial_fn(Q, K_local, V_local, scale, causal, k0, skv_total)
+    else:
+        # a rank without keys (more ranks than 128-key blocks) launches nothing and still joins the exchange, with an
+        # empty partial result: (m, l) = (-inf, 0) for every row, which the combine skips (the accumulators are not read)
+        part = empty_partial(Q.shape[0] * Q.shape[1] * Q.shape[2], Q.shape[3], Q.device)
     gathered = torch.empty((world, part.numel()), dtype=torch.uint8, device=part.device)
     dist.all_gather_into_tensor(gathered, part.view(1, -1), group=group)
-    # a rank without keys (more ranks than key blocks) contributes l = 0 rows, which the combine skips
     return combine_fn(gathered, tuple(Q.shape))
+
+
+def empty_partial(rows: int, D: int, device):
+    """Partial result of a KV share with no key, in the byte layout of ``axp_sm100_attn_fwd_bf16_kvshard``:
+    ``rows * D`` fp32 accumulators, then ``rows`` pairs (m, l) = (-inf, 0)."""
+    import torch
+
+    part = torch.zeros(rows * (D * 4 + 8), dtype=torch.uint8, device=device)
+    ml = part[rows * D * 4:].view(torch.float32).view(rows, 2)
+    ml[:, 0] = float("-inf")
+    return part

@@ -120,6 +120,15 @@ void oracle_bf16_encode(const float* in, uint16_t* out, int64_t n) {
     for (int64_t i = 0; i < n; ++i) out[i] = f32_to_bf16(in[i]);
 }
 
+// Launchers that export OMP_NUM_THREADS=1 would otherwise leave the oracle on one core.
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -379,7 +388,7 @@ void oracle_quantize_rows_e4m3(const uint16_t* X, uint8_t* Q, float* scales, int
         for (int64_t kb = 0; kb < KB; ++kb) {
             float amax = 0.0f;
             for (int k = 0; k < 128; ++k) amax = std::max(amax, std::fabs(bf16_to_f32(X[m * ldx + kb * 128 + k])));
-            const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+            const float scale = amax > 0.0f ? std::max(amax / 448.0f, 1.17549435e-38f) : 1.0f;   // floor: 1 / scale stays finite
             const float inv = 1.0f / scale;
             for (int k = 0; k < 128; ++k) Q[m * ldq + kb * 128 + k] = f32_to_e4m3_sat(bf16_to_f32(X[m * ldx + kb * 128 + k]) * inv);
             scales[m * KB + kb] = scale;
@@ -431,7 +440,7 @@ void oracle_rmsnorm_quantize_rows_e4m3(const uint16_t* X, const uint16_t* W, flo
                 y[k] = xs * bf16_to_f32(W[kb * 128 + k]);
                 amax = std::max(amax, std::fabs(y[k]));
             }
-            const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+            const float scale = amax > 0.0f ? std::max(amax / 448.0f, 1.17549435e-38f) : 1.0f;   // floor: 1 / scale stays finite
             const float inv = 1.0f / scale;
             for (int k = 0; k < 128; ++k) Q[m * ldq + kb * 128 + k] = f32_to_e4m3_sat(y[k] * inv);
             scales[m * KB + kb] = scale;

@@ -50,6 +50,11 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the following calls (a launcher may have exported OMP_NUM_THREADS=1)."""
+    lib().oracle_set_num_threads(ctypes.c_int(int(n)))
+
+
 def e4m3_decode(b: np.ndarray) -> np.ndarray:
     b = np.ascontiguousarray(b, dtype=np.uint8)
     out = np.empty(b.shape, dtype=np.float32)

@@ -63,6 +63,16 @@ def test_bad_arguments_return_codes_without_touching_a_gpu(pkg, lib):
     assert rc == pkg.capi.AXP_ERR_BAD_ARG                                               # n_end > N
     rc = lib.axp_sm100_gemm_bf16(ctypes.c_void_p(4100), p, p, 128, 128, 128, 128, 128, 128, 0, 128, z, z)
     assert rc == pkg.capi.AXP_ERR_BAD_ARG                                               # misaligned base
+    # a column range that does not span a multiple of 8 columns would let the 8-wide epilogue stores run into the
+    # neighbouring shard: rejected by every GEMM entry point
+    rc = lib.axp_sm100_gemm_bf16(p, p, p, 128, 256, 128, 128, 128, 256, 0, 100, z, z)
+    assert rc == pkg.capi.AXP_ERR_BAD_ARG and b"multiple of 8" in lib.axp_sm100_last_error()
+    rc = lib.axp_sm100_gemm_fp8_blockscaled(p, p, p, p, p, 128, 256, 256, 256, 256, 256, 128, 228, z, z)
+    assert rc == pkg.capi.AXP_ERR_BAD_ARG and b"multiple of 8" in lib.axp_sm100_last_error()
+    rc = lib.axp_sm100_gemm_bf16_swiglu(p, p, p, p, 128, 256, 128, 128, 128, 128, 256, 0, 100, z, z)
+    assert rc == pkg.capi.AXP_ERR_BAD_ARG and b"multiple of 8" in lib.axp_sm100_last_error()
+    rc = lib.axp_sm100_gemm_fp8_blockscaled_swiglu(p, p, p, p, p, p, p, 128, 256, 256, 256, 256, 256, 256, 0, 100, z, z)
+    assert rc == pkg.capi.AXP_ERR_BAD_ARG and b"multiple of 8" in lib.axp_sm100_last_error()
     rc = lib.axp_sm100_attn_fwd_bf16(p, p, p, p, z, 1, 4, 3, 128, 128, ctypes.c_float(1.0), 1, 0, 4, z, z)
     assert rc == pkg.capi.AXP_ERR_BAD_ARG                                               # Hq % Hkv
     rc = lib.axp_sm100_attn_fwd_bf16(p, p, p, p, z, 1, 4, 4, 128, 64, ctypes.c_float(1.0), 1, 0, 4, z, z)

@@ -19,7 +19,10 @@ def _worker(rank, world, port, q):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import datetime
+
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
     try:
         pkg = importlib.import_module("iro-cuda-ax_b200")
         from oracle import host_oracle as oracle
@@ -46,15 +49,27 @@ def _worker(rank, world, port, q):
 def test_kv_sharded_attention_on_two_gpus():
     import torch.multiprocessing as mp
 
+    import socket
+
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + (os.getpid() % 1000) + 11
+    with socket.socket() as s:           # a free port: concurrent jobs on one machine must not meet at the same rendezvous
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(300)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.join(300)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:                  # a stuck rank must not keep holding its GPU after the test
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
     for _ in range(2):
         rank, out = q.get(timeout=5)
         for err, lerr in out:

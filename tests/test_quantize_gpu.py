@@ -61,6 +61,24 @@ def test_quantize_then_fp8_gemm_tracks_bf16_gemm(pkg, dev):
     assert rel < 5e-2
 
 
+def test_quantize_tiny_block_with_zeros_has_no_nan(pkg, oracle, dev):
+    """A block whose largest magnitude is of denormal size (1 / scale would overflow) and that also holds exact zeros:
+    the scale is floored at the smallest normal float, no code is the E4M3 NaN (0x7f / 0xff), and codes and scales
+    still equal the oracle's bit for bit."""
+    X = torch.zeros(4, 256, dtype=torch.bfloat16)
+    X[0, 3] = 1e-38
+    X[1, 130] = -3e-39          # a bf16 denormal
+    X[2, :128] = 9.2e-41        # the smallest bf16 denormal everywhere in the block
+    X[3, 5] = 1.0
+    Q, S = pkg.ops.quantize_rows_e4m3(X.to(dev))
+    Qw, Sw = oracle.quantize_rows_e4m3(X.view(torch.uint16).numpy())
+    q = Q.view(torch.uint8).cpu().numpy()
+    assert not np.any((q & 0x7f) == 0x7f)
+    assert np.all(np.isfinite(S.cpu().numpy())) and np.all(S.cpu().numpy() > 0)
+    assert np.array_equal(q, Qw)
+    assert np.array_equal(S.cpu().numpy().view(np.uint32), Sw.view(np.uint32))
+
+
 def test_quantize_argument_errors(pkg, dev):
     with pytest.raises(pkg.capi.AxpError) as e:
         pkg.ops.quantize_rows_e4m3(torch.zeros(4, 200, dtype=torch.bfloat16, device=dev))

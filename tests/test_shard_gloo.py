@@ -55,7 +55,7 @@ def test_attention_head_ranges_keep_kv_groups_whole(pkg):
         assert prev == B * Hq
 
 
-def _kv_sharded_worker(rank, world, port, q):
+def _kv_sharded_worker(rank, world, port, q, Skv=320):
     import importlib
     import os
     import sys
@@ -71,7 +71,7 @@ def _kv_sharded_worker(rank, world, port, q):
         pkg = importlib.import_module("iro-cuda-ax_b200")
         from oracle import host_oracle as oracle
 
-        B, Hq, Hkv, Sq, Skv, D = 1, 4, 2, 24, 320, 128
+        B, Hq, Hkv, Sq, D = 1, 4, 2, 24, 128
         Q, _, _, scale = pkg.synth.bf16_attention_inputs(B, Hq, Sq, D, seed=3, Hkv=Hkv)
         _, K, V, _ = pkg.synth.bf16_attention_inputs(B, Hkv, Skv, D, seed=4)
         k0, k1 = pkg.shard.kv_shard_range(Skv, world, rank)
@@ -133,16 +133,47 @@ def test_kv_sharded_attention_exchange_world_size_2():
     results in the C-ABI byte layout, and the state combine, with CPU stand-ins for the two CUDA entry points."""
     import torch.multiprocessing as mp
 
+    got = _run_kv_sharded(2, 320)
+    assert [g[1] for g in got] == [(0, 256), (256, 320)]         # 128-key blocks: three blocks over two ranks
+    for _, _, err, lerr in got:
+        assert err <= 1e-2 and lerr <= 1e-4
+
+
+def _free_port():
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run_kv_sharded(world, Skv):
+    import torch.multiprocessing as mp
+
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + (os.getpid() % 1000) + 7
-    procs = [ctx.Process(target=_kv_sharded_worker, args=(r, 2, port, q)) for r in range(2)]
+    port = _free_port()
+    procs = [ctx.Process(target=_kv_sharded_worker, args=(r, world, port, q, Skv)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(120)
-        assert p.exitcode == 0
-    got = sorted(q.get(timeout=5) for _ in range(2))
-    assert [g[1] for g in got] == [(0, 256), (256, 320)]         # 128-key blocks: three blocks over two ranks
+    try:
+        for p in procs:
+            p.join(180)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:                  # no child outlives the test, whatever happened
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+    return sorted(q.get(timeout=5) for _ in range(world))
+
+
+def test_kv_sharded_attention_rank_without_keys_still_joins_the_exchange():
+    """More ranks than 128-key blocks: the last rank holds no key, launches nothing and contributes an empty partial
+    result, so that every rank enters the all-gather and the combined result is still the full attention."""
+    got = _run_kv_sharded(3, 256)
+    assert [g[1] for g in got] == [(0, 128), (128, 256), (256, 256)]
     for _, _, err, lerr in got:
         assert err <= 1e-2 and lerr <= 1e-4
