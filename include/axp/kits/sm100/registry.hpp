@@ -10,6 +10,7 @@
 
 #include "../../protocol/sm100_contracts.hpp"
 #include "../../realize/sm100.hpp"
+#include "../../realize/sm100_host.hpp"
 #include "../../realize/sm100_mask.hpp"
 
 namespace axp::kit::sm100 {
@@ -41,15 +42,28 @@ struct registry_for {
 #define AXP_T(...) template <__VA_ARGS__>
 #define AXP_O(...) __VA_ARGS__
 
-struct HostTensorMapEncoder {};   // host side: cuTensorMapEncodeTiled through the driver entry point (launch shim)
-struct ScalePromoteFma {};        // fmaf(sA*sB, partial, acc) in the epilogue warps (gemm kernel)
-struct RowStoreVec16 {};          // 16-byte row stores of packed bf16 (gemm / attention epilogues)
-struct RowSoftmaxExp2 {};
-struct BiasActFma {};           // acc + bias, then x / (1 + __expf(-x)) for SiLU, before the bf16 pack (gemm epilogue)         // ex2.approx based row update (attention kernel)
+// Every leaf carries its code in a member named `execute` (possibly overloaded or a template).  Detection by name:
+// a class that inherits both the leaf and a fallback with a data member `execute` makes `&D::execute` ambiguous
+// exactly when the leaf has a member of that name.
+namespace detail {
+struct execute_fallback {
+    int execute;
+};
+template <class L>
+struct execute_probe : L, execute_fallback {};
+template <class L, class = void>
+struct has_execute : std::true_type {};
+template <class L>
+struct has_execute<L, std::void_t<decltype(&execute_probe<L>::execute)>> : std::false_type {};
+template <class List>
+struct all_have_execute;
+template <class... Ls>
+struct all_have_execute<type_list<Ls...>> : std::bool_constant<(sizeof...(Ls) > 0) && (has_execute<Ls>::value && ...)> {};
+}  // namespace detail
 
 #if defined(__CUDACC__)
 AXP_SM100_REGISTER(AXP_T(class S, class E, int R), AXP_O(px::HostMakeTensorMap<S, E, R>), "tma.host_make_tensor_map",
-                   HostTensorMapEncoder);
+                   rz::HostTensorMapEncoder);
 AXP_SM100_REGISTER(AXP_T(class S, int B, int N), AXP_O(px::StageRing<S, B, N, 2>), "stage.ring_2d", rz::BarrierInit,
                    rz::BarrierExpectTx, rz::BulkTmaCopy2D, rz::BarrierWait, rz::MakeSmemDescKMajorSw128);
 AXP_SM100_REGISTER(AXP_T(class S, int B, int N), AXP_O(px::StageRing<S, B, N, 3>), "stage.ring_3d", rz::BarrierInit,
@@ -69,19 +83,21 @@ AXP_SM100_REGISTER(AXP_T(int C), AXP_O(px::TmemToRegisters<C>), "tmem.ld_32x32b"
                    rz::Tcgen05FenceBefore);
 AXP_SM100_REGISTER(AXP_T(int C), AXP_O(px::RegistersToTmem<C>), "tmem.st_32x32b", rz::TmemStore32x32, rz::TmemStoreWait,
                    rz::Tcgen05FenceBefore);
-AXP_SM100_REGISTER(AXP_T(class R), AXP_O(px::ScalePromoteAccumulator<R>), "scale.promote_fma", ScalePromoteFma);
+AXP_SM100_REGISTER(AXP_T(int B, int N), AXP_O(px::RegistersToSharedOperand<B, N>), "stage.registers_to_shared_operand", rz::AsyncProxyFence,
+                   rz::BarrierArrive, rz::MakeSmemDescKMajorSw128);
+AXP_SM100_REGISTER(AXP_T(class R), AXP_O(px::ScalePromoteAccumulator<R>), "scale.promote_fma", rz::ScalePromoteFma);
 AXP_SM100_REGISTER(AXP_T(class P), AXP_O(px::CastPack<iro::elem::f32, iro::elem::bf16, P>), "convert.pack_bf16x2",
                    rz::PackBf16x2);
 AXP_SM100_REGISTER(AXP_T(class P), AXP_O(px::CastPack<iro::elem::f32, iro::elem::e4m3, P>), "convert.pack_e4m3x4_sat",
                    rz::PackE4m3x4);
 AXP_SM100_REGISTER(AXP_T(class P), AXP_O(px::CastWeights<iro::elem::bf16, P>), "convert.weights_bf16x2", rz::PackBf16x2);
 AXP_SM100_REGISTER(AXP_T(class P), AXP_O(px::CastWeights<iro::elem::e4m3, P>), "convert.weights_e4m3x4_sat", rz::PackE4m3x4);
-AXP_SM100_REGISTER(AXP_T(class B, class A), AXP_O(px::BiasActivation<B, A>), "epilogue.bias_activation", BiasActFma);
-AXP_SM100_REGISTER(AXP_T(class U, class A), AXP_O(px::GatedActivation<U, A>), "epilogue.gated_activation", BiasActFma);
-AXP_SM100_REGISTER(AXP_T(class C, class A, class B), AXP_O(px::LinearCombination<C, A, B>), "epilogue.linear_combination", BiasActFma);
-AXP_SM100_REGISTER(AXP_T(class E), AXP_O(px::StoreRowGlobal<E>), "store.row_vec16", RowStoreVec16);
-AXP_SM100_REGISTER(AXP_T(int M, int N), AXP_O(px::CausalMaskPredicate<M, N>), "mask.causal_pred");
-AXP_SM100_REGISTER(template <>, px::RowSoftmaxStateUpdate, "softmax.row_state_exp2", RowSoftmaxExp2);
+AXP_SM100_REGISTER(AXP_T(class B, class A), AXP_O(px::BiasActivation<B, A>), "epilogue.bias_activation", rz::BiasActFma);
+AXP_SM100_REGISTER(AXP_T(class U, class A), AXP_O(px::GatedActivation<U, A>), "epilogue.gated_activation", rz::BiasActFma);
+AXP_SM100_REGISTER(AXP_T(class C, class A, class B), AXP_O(px::LinearCombination<C, A, B>), "epilogue.linear_combination", rz::BiasActFma);
+AXP_SM100_REGISTER(AXP_T(class E), AXP_O(px::StoreRowGlobal<E>), "store.row_vec16", rz::RowStoreVec16);
+AXP_SM100_REGISTER(AXP_T(int M, int N), AXP_O(px::CausalMaskPredicate<M, N>), "mask.causal_pred", rz::CausalMaskPred);
+AXP_SM100_REGISTER(template <>, px::RowSoftmaxStateUpdate, "softmax.row_state_exp2", rz::RowSoftmaxExp2);
 AXP_SM100_REGISTER(template <>, px::RescaleAccumulatorInTmem, "softmax.rescale_tmem", rz::TmemLoad32x32, rz::TmemStore32x32,
                    rz::TmemStoreWait);
 AXP_SM100_REGISTER(AXP_T(int P, int M), AXP_O(px::RoleRegisterBudget<P, M>), "specialize.setmaxnreg", rz::RegDealloc<P>,
@@ -100,9 +116,11 @@ using registry_for_t = typename registry_for<O>::type;
 template <class O>
 using bind = iro::bind::lookup_realization_t<O, iro::cap::sm100, registry_for_t<O>>;
 
+// every obligation of the list binds, and every leaf of every bound realization has an execute member
 template <class List>
 struct binds_all;
 template <class... Os>
-struct binds_all<type_list<Os...>> : std::bool_constant<(bind<Os>::found && ...)> {};
+struct binds_all<type_list<Os...>>
+    : std::bool_constant<((bind<Os>::found && detail::all_have_execute<typename bind<Os>::realization::leaves>::value) && ...)> {};
 
 }  // namespace axp::kit::sm100

@@ -4,11 +4,12 @@
 
 namespace preset {
 
-// bf16 flash-attention forward tile: 128 queries x 128 keys, head dim 128, causal skip.
+// bf16 flash-attention forward tile: 128 queries x 128 keys, head dim 128, causal skip; four K/V stages (of the
+// 64-key steps the realization takes a tile in).
 using Attention128x128x128CausalBf16 = axp::l4::AttentionPattern<
     axp::recipe::BF16AccF32Fast,
     128, 128, 128, 128,
-    2, 0,
+    4, 0,
     AttnQ, AttnK, AttnV,
     AttnAcc, AttnStateOld, AttnStateNew,
     axp::intent::memory_pattern::Optimized,
@@ -25,7 +26,7 @@ using Attention128x128x128CausalBf16 = axp::l4::AttentionPattern<
 using Attention128x128x128CausalFp8Gqa = axp::l4::AttentionPattern<
     axp::recipe::E4M3AccF32OutBF16,
     128, 128, 128, 128,
-    4, 0,
+    3, 0,
     AttnQ, AttnK, AttnV,
     AttnAcc, AttnStateOld, AttnStateNew,
     axp::intent::memory_pattern::Optimized,

@@ -5,11 +5,11 @@
 
 namespace preset {
 
-// FP8 E4M3 block-scaled GEMM, CTA tile 128 x 256, 128-wide K blocks, bf16 out.
+// FP8 E4M3 block-scaled GEMM, CTA tile 128 x 256 (CTA pairs: 256 x 256 per cluster), 128-wide K blocks, bf16 out.
 using GemmFp8BlockScaled128x256x128 = axp::l4::GemmPattern<
     axp::recipe::E4M3BlockScaledAccF32OutBF16,
     128, 256, 128,
-    4, 5,
+    6, 7,
     GemmA, GemmB, GemmC,
     GemmAcc,
     axp::intent::memory_pattern::Optimized,

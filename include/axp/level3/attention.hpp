@@ -3,12 +3,13 @@
 // Reference dataflow per (Q tile, KV tile) step (include/axp/level3/recipes/
 // attention/process.hpp:1766-1864): QK -> mask -> softmax(+state) -> combine ->
 // rescale accumulator -> scale weights -> cast P -> PV -> add.  The sm100 graph
-// keeps the same steps with the softmax state per query row, S / P / O in tensor
-// memory (P is the tensor-memory A operand of the PV MMA, V its MN-major B
-// operand), and the accumulator rescale applied in place only when a row maximum
-// grew.  The reference restricts attention inputs to f16/bf16
+// keeps the same steps with the softmax state per query row, S and O in tensor
+// memory, P either overwriting its S region (16-bit: the tensor-memory A operand of
+// the PV MMA) or passing through shared memory (8-bit), V the MN-major B operand,
+// and the accumulator rescale applied in place only when a row maximum grew.  The reference restricts attention inputs to f16/bf16
 // (include/axp/level3/attention.hpp:95-96); the E4M3 branch is an sm100 addition.
 #pragma once
+#include "../kits/intent.hpp"
 #include "../kits/sm100/index.hpp"
 #include "../protocol/sm100_contracts.hpp"
 #include "../state.hpp"
@@ -18,37 +19,76 @@ namespace axp::level3 {
 
 namespace px = axp::protocol::sm100;
 
+struct attention_pipe_tag {
+    static constexpr auto id = iro::util::fnv1a_64_cstr("axp.level3.attention.sm100.pipe");
+};
+struct attention_p_tag {
+    static constexpr auto id = iro::util::fnv1a_64_cstr("axp.level3.attention.sm100.p");
+};
+
 template <class Recipe, int TileQ, int TileK, int TileV, int HeadDim, int Stages, class QSubj, class KSubj, class VSubj,
-          class TileSkip, class Cap>
+          class MemoryPatternQ, class MemoryPatternK, class MemoryPatternV, class LoadModeQ, class LoadModeK, class LoadModeV,
+          class Schedule, class TileSkip, class Cap>
 struct AttentionTileTcgen05Impl {
     using in = typename Recipe::in_a;
     using out = typename Recipe::out;
     static_assert(TileK == TileV, "K and V tiles cover the same keys (reference attention.hpp:808)");
     static_assert(TileQ == 128 && TileK == 128 && HeadDim == 128, "realised tile: 128 queries x 128 keys x 128 head dim");
     static_assert(Stages >= 2 && Stages <= 4, "2..4 K/V stages");
+
+    // ---- intents -> mechanisms ----
+    // Q and K rows are HeadDim elements (K-major operands of Q.K^T), V rows are its MN-major B operand: all are staged
+    // as 128-byte swizzle spans by TMA.
+    using q_swizzle = axp::kit::detail::select_swizzle_t<MemoryPatternQ, in, HeadDim, Cap, true>;
+    using k_swizzle = axp::kit::detail::select_swizzle_t<MemoryPatternK, in, HeadDim, Cap, true>;
+    using v_swizzle = axp::kit::detail::select_swizzle_t<MemoryPatternV, in, HeadDim, Cap, false>;
+    static_assert(q_swizzle::span_bytes == 128 && k_swizzle::span_bytes == 128 && v_swizzle::span_bytes == 128,
+                  "the sm100 attention stages 128-byte swizzle spans: memory_pattern::Optimized");
+    using q_tma = axp::kit::detail::select_tma_t<LoadModeQ, Cap, void, QSubj, attention_pipe_tag>;
+    using k_tma = axp::kit::detail::select_tma_t<LoadModeK, Cap, void, KSubj, attention_pipe_tag>;
+    using v_tma = axp::kit::detail::select_tma_t<LoadModeV, Cap, void, VSubj, attention_pipe_tag>;
+    static_assert(axp::kit::detail::is_tma_config_v<q_tma> && axp::kit::detail::is_tma_config_v<k_tma> && axp::kit::detail::is_tma_config_v<v_tma>,
+                  "the sm100 attention loads Q, K and V by TMA: load_mode::AsyncPrefetch on a TMA target");
+    using schedule = axp::kit::detail::select_schedule_t<Schedule, Cap>;
+
     static constexpr int kQTilesPerCta = 2;
     static constexpr int kMmaK = 32 / in::bytes;
-    static constexpr int kTileBytes = 128 * HeadDim * in::bytes;
+    // 16-bit operands: the 128 keys of the intent tile are taken in two steps of 64 (two 64-column S buffers per Q tile,
+    // so that the next Q.K^T is in flight while the softmax runs) and P overwrites its S region in tensor memory.
+    // 8-bit operands: steps of 128 keys, P goes to the P.V MMA through shared memory (two tiles per Q tile).
+    static constexpr bool kPThroughSmem = in::bytes == 1;
+    static constexpr int kKvStep = in::bytes == 2 ? 64 : 128;
+    static constexpr int kQTileBytes = TileQ * HeadDim * in::bytes;
+    static constexpr int kKvTileBytes = kKvStep * HeadDim * in::bytes;
     static constexpr int kTmemCols = 512;   // S0 S1 O0 O1, 128 fp32 columns each
-    static constexpr int kThreads = 384;
+    static constexpr int kThreads = 384;    // two softmax warpgroups (one per Q tile), TMA producer warp, two issuing warps
+    static constexpr int kProducerRegs = 56, kSoftmaxRegs = 224;
+    static constexpr int kIssuers = 2;
     static constexpr bool causal = std::is_same_v<TileSkip, axp::intent::tile_skip::Causal>;
 
-    using qk = px::Tcgen05Mma<TileQ, TileK, kMmaK, in, in, 1, px::OperandSource::shared, px::Major::k>;
-    using pv = px::Tcgen05Mma<TileQ, HeadDim, kMmaK, in, in, 1, px::OperandSource::tmem, px::Major::mn>;
+    using qk = px::Tcgen05Mma<TileQ, kKvStep, kMmaK, in, in, 1, px::OperandSource::shared, px::Major::k>;
+    using pv = px::Tcgen05Mma<TileQ, HeadDim, kMmaK, in, in, 1, (kPThroughSmem ? px::OperandSource::shared : px::OperandSource::tmem),
+                              px::Major::mn>;
+    using p_route = std::conditional_t<kPThroughSmem, px::RegistersToSharedOperand<kQTileBytes, 2 * kQTilesPerCta>, px::RegistersToTmem<32>>;
     using obligations = iro::util::type_list<
         px::HostMakeTensorMap<QSubj, in, 3>, px::HostMakeTensorMap<KSubj, in, 3>, px::HostMakeTensorMap<VSubj, in, 3>,
-        px::StageRing<QSubj, kTileBytes, kQTilesPerCta, 3>, px::StageRing<KSubj, kTileBytes, Stages, 3>,
-        px::StageRing<VSubj, kTileBytes, Stages, 3>, px::RoleRegisterBudget<40, 232>, px::TmemAllocate<kTmemCols, 1>,
-        px::BoundedBarrierWait, qk, px::Tcgen05Commit<1>, px::TmemToRegisters<32>, px::CausalMaskPredicate<TileQ, TileK>,
+        px::StageRing<QSubj, kQTileBytes, kQTilesPerCta, 3>, px::StageRing<KSubj, kKvTileBytes, Stages, 3>,
+        px::StageRing<VSubj, kKvTileBytes, Stages, 3>, px::RoleRegisterBudget<kProducerRegs, kSoftmaxRegs>, px::TmemAllocate<kTmemCols, 1>,
+        px::BoundedBarrierWait, qk, px::Tcgen05Commit<1>, px::TmemToRegisters<32>, px::CausalMaskPredicate<TileQ, kKvStep>,
         px::RowSoftmaxStateUpdate, px::RescaleAccumulatorInTmem, px::CastWeights<in, typename Recipe::fp8_policy>,
-        px::RegistersToTmem<32>, pv, px::CastPack<iro::elem::f32, out, typename Recipe::fp8_policy>, px::StoreRowGlobal<out>,
+        p_route, pv, px::CastPack<iro::elem::f32, out, typename Recipe::fp8_policy>, px::StoreRowGlobal<out>,
         px::TmemRelease<kTmemCols, 1>>;
 
-    struct type : iro::compose::Composition<obligations, Cap, kThreads, 232> {
+    struct type : iro::compose::Composition<obligations, Cap, kThreads, kSoftmaxRegs> {
         using recipe = Recipe;
         using state = axp::state::SoftmaxStateF32;
         static constexpr int tile_q = TileQ, tile_k = TileK, head_dim = HeadDim, stages = Stages;
+        static constexpr int kv_step = kKvStep, q_tiles = kQTilesPerCta, issuers = kIssuers;
+        static constexpr int producer_regs = kProducerRegs, softmax_regs = kSoftmaxRegs;
+        static constexpr bool p_through_smem = kPThroughSmem;
         static constexpr bool is_causal = causal;
+        using q_swizzle = typename AttentionTileTcgen05Impl::q_swizzle;
+        using schedule = typename AttentionTileTcgen05Impl::schedule;
     };
     static_assert(axp::kit::sm100::binds_all<obligations>::value, "every obligation needs an sm100 realization");
 };
@@ -61,7 +101,8 @@ template <class Recipe, int TQ, int TK, int TV, int HD, int Stages, int SlotIdx,
 struct resolve_impl<AttentionTilePattern<Recipe, TQ, TK, TV, HD, Stages, SlotIdx, QSubj, KSubj, VSubj, AccSubj, OldS, OutS, MPQ,
                                          MPK, MPV, LMQ, LMK, LMV, Schedule, TileSkip, QTma, KTma, VTma>,
                     Cap, std::enable_if_t<Cap::has_tcgen05>> {
-    using type = typename AttentionTileTcgen05Impl<Recipe, TQ, TK, TV, HD, Stages, QSubj, KSubj, VSubj, TileSkip, Cap>::type;
+    using type = typename AttentionTileTcgen05Impl<Recipe, TQ, TK, TV, HD, Stages, QSubj, KSubj, VSubj, MPQ, MPK, MPV, LMQ, LMK, LMV, Schedule,
+                                                   TileSkip, Cap>::type;
 };
 
 }  // namespace registry

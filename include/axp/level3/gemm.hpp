@@ -10,6 +10,7 @@
 // rows to global memory.  KTiles is the window length; the runtime K loop and the
 // tile scheduler belong to the kernel.
 #pragma once
+#include "../kits/intent.hpp"
 #include "../kits/sm100/index.hpp"
 #include "../naming/subjects.hpp"
 #include "../protocol/sm100_contracts.hpp"
@@ -20,23 +21,49 @@ namespace axp::level3 {
 
 namespace px = axp::protocol::sm100;
 
+struct gemm_pipe_tag {
+    static constexpr auto id = iro::util::fnv1a_64_cstr("axp.level3.gemm.sm100.pipe");
+};
+
 template <class Recipe, int BlockM, int BlockN, int BlockK, int Stages, class ASubj, class BSubj, class CSubj, class Cap,
+          class MemoryPatternA, class MemoryPatternB, class LoadModeA, class LoadModeB, class Schedule,
           class EpiloguePolicy = epilogue::None>
 struct GemmTileTcgen05Impl {
     using in_a = typename Recipe::in_a;
     using in_b = typename Recipe::in_b;
     using out = typename Recipe::out;
     static_assert(std::is_same_v<typename Recipe::acc, iro::elem::f32>, "tcgen05 accumulates in fp32");
-    static_assert(BlockK * in_a::bytes == 128, "one stage row is one 128-byte swizzle span of K");
     static_assert(Stages >= 2 && Stages <= 8, "2..8 shared-memory stages");
+
+    // ---- intents -> mechanisms (axp::kit::detail selectors, expert overrides included) ----
+    // Both operands are K-major rows of BlockK elements.  The realization stages 128-byte swizzled rows by TMA and runs
+    // as a warp-specialised producer / issuer / epilogue pipeline; intents that select anything else have no sm100
+    // realization.
+    using a_swizzle = axp::kit::detail::select_swizzle_t<MemoryPatternA, in_a, BlockK, Cap, true>;
+    using b_swizzle = axp::kit::detail::select_swizzle_t<MemoryPatternB, in_b, BlockK, Cap, false>;
+    static_assert(a_swizzle::span_bytes == 128 && b_swizzle::span_bytes == 128,
+                  "the sm100 GEMM stages rows of one 128-byte swizzle span: memory_pattern::Optimized with BlockK * bytes == 128");
+    static_assert(BlockK * in_a::bytes == 128, "one stage row is one 128-byte swizzle span of K");
+    using a_tma = axp::kit::detail::select_tma_t<LoadModeA, Cap, void, ASubj, gemm_pipe_tag>;
+    using b_tma = axp::kit::detail::select_tma_t<LoadModeB, Cap, void, BSubj, gemm_pipe_tag>;
+    static_assert(axp::kit::detail::is_tma_config_v<a_tma> && axp::kit::detail::is_tma_config_v<b_tma>,
+                  "the sm100 GEMM loads its operands by TMA: load_mode::AsyncPrefetch on a TMA target");
+    using schedule = axp::kit::detail::select_schedule_t<Schedule, Cap>;
+    static_assert(std::is_same_v<schedule, axp::intent::schedule::ProducerConsumer> ||
+                      std::is_same_v<schedule, axp::intent::schedule::PersistentPipeline> ||
+                      std::is_same_v<schedule, axp::intent::schedule::Pipelined>,
+                  "the sm100 GEMM is a persistent producer / consumer pipeline");
+
     static constexpr int kMmaK = 32 / in_a::bytes;
-    // Scaled recipes hand the accumulator to the epilogue once per K block, which does not
-    // tolerate the latency of a CTA pair: one CTA per MMA.  Unscaled recipes use CTA pairs
-    // (cta_group::2): a 2*BlockM x BlockN MMA, each CTA loading its own half of A and of B.
-    static constexpr int kCtaGroup = Recipe::has_scales ? 1 : 2;
+    // CTA pairs (cta_group::2): a 2*BlockM x BlockN MMA, each CTA loading its own half of A and of B.  Scaled recipes
+    // hand the accumulator to the epilogue once per K block; the remote arrive of that hand-over is a relaxed one.
+    static constexpr int kCtaGroup = 2;
     static constexpr int kAccStages = 2;
     static constexpr int kTmemCols = kAccStages * BlockN;
+    // scaled: two epilogue warpgroups (a thread carries the BlockN / 2 running sums of its row); else four
     static constexpr int kThreads = Recipe::has_scales ? 384 : 640;
+    static constexpr int kProducerRegs = Recipe::has_scales ? 40 : 32;
+    static constexpr int kEpilogueRegs = Recipe::has_scales ? 232 : 112;
     static constexpr int kABytes = BlockM * BlockK * in_a::bytes;
     static constexpr int kBBytes = BlockN / kCtaGroup * BlockK * in_b::bytes;
     static_assert(Stages * (kABytes + kBBytes) <= Cap::max_smem_bytes, "stage ring exceeds shared memory");
@@ -45,7 +72,7 @@ struct GemmTileTcgen05Impl {
     using base = iro::util::type_list<
         px::HostMakeTensorMap<ASubj, in_a, 2>, px::HostMakeTensorMap<BSubj, in_b, 2>,
         px::StageRing<ASubj, kABytes, Stages, 2>, px::StageRing<BSubj, kBBytes, Stages, 2>,
-        px::RoleRegisterBudget<(Recipe::has_scales ? 40 : 32), (Recipe::has_scales ? 232 : 112)>, px::TmemAllocate<kTmemCols, kCtaGroup>, px::BoundedBarrierWait, mma,
+        px::RoleRegisterBudget<kProducerRegs, kEpilogueRegs>, px::TmemAllocate<kTmemCols, kCtaGroup>, px::BoundedBarrierWait, mma,
         px::Tcgen05Commit<kCtaGroup>, px::TmemToRegisters<32>>;
     using scale = std::conditional_t<Recipe::has_scales, iro::util::type_list<px::ScalePromoteAccumulator<Recipe>>,
                                      iro::util::type_list<>>;
@@ -79,6 +106,11 @@ struct GemmTileTcgen05Impl {
     struct type : iro::compose::Composition<obligations, Cap, kThreads, 232> {
         using recipe = Recipe;
         static constexpr int block_m = BlockM, block_n = BlockN, block_k = BlockK, stages = Stages;
+        static constexpr int cta_group = kCtaGroup, producer_regs = kProducerRegs, epilogue_regs = kEpilogueRegs;
+        using a_swizzle = typename GemmTileTcgen05Impl::a_swizzle;
+        using b_swizzle = typename GemmTileTcgen05Impl::b_swizzle;
+        using a_tma = typename GemmTileTcgen05Impl::a_tma;
+        using schedule = typename GemmTileTcgen05Impl::schedule;
         static constexpr int mma_per_stage = BlockK / kMmaK;
         static constexpr bool scaled = Recipe::has_scales;
         static constexpr bool fused_epilogue = EpiloguePolicy::enabled;
@@ -94,7 +126,7 @@ template <class Recipe, int BM, int BN, int BK, int Stages, int KTiles, class AS
 struct resolve_impl<GemmTilePattern<Recipe, BM, BN, BK, Stages, KTiles, ASubj, BSubj, CSubj, WgmmaSubj, MPA, MPB, LMA, LMB,
                                     Schedule, ScaleASubj, ScaleBSubj, ATma, BTma>,
                     Cap, std::enable_if_t<Cap::has_tcgen05>> {
-    using type = typename GemmTileTcgen05Impl<Recipe, BM, BN, BK, Stages, ASubj, BSubj, CSubj, Cap>::type;
+    using type = typename GemmTileTcgen05Impl<Recipe, BM, BN, BK, Stages, ASubj, BSubj, CSubj, Cap, MPA, MPB, LMA, LMB, Schedule>::type;
 };
 
 template <class Recipe, int BM, int BN, int BK, int Stages, int KTiles, class ASubj, class BSubj, class CSubj, class WgmmaSubj,
@@ -103,7 +135,7 @@ template <class Recipe, int BM, int BN, int BK, int Stages, int KTiles, class AS
 struct resolve_impl<GemmTileFusedPattern<Recipe, BM, BN, BK, Stages, KTiles, ASubj, BSubj, CSubj, WgmmaSubj, Epi, MPA, MPB, LMA,
                                          LMB, Schedule, ScaleASubj, ScaleBSubj, ATma, BTma>,
                     Cap, std::enable_if_t<Cap::has_tcgen05>> {
-    using type = typename GemmTileTcgen05Impl<Recipe, BM, BN, BK, Stages, ASubj, BSubj, CSubj, Cap, Epi>::type;
+    using type = typename GemmTileTcgen05Impl<Recipe, BM, BN, BK, Stages, ASubj, BSubj, CSubj, Cap, MPA, MPB, LMA, LMB, Schedule, Epi>::type;
 };
 
 }  // namespace registry

@@ -136,6 +136,15 @@ struct LinearCombination
     using beta_subject = BetaSubj;
 };
 
+// Registers -> a 128-byte-swizzled operand tile in shared memory (`Slots` tiles of `TileBytes`), made visible to the
+// tensor core with a proxy fence: the route of the E4M3 softmax weights P to the P.V MMA (the S region in tensor memory
+// is then free as soon as the softmax holds it in registers).
+template <int TileBytes, int Slots>
+struct RegistersToSharedOperand : Obligation<mix_u64(fnv1a_64_cstr("axp.protocol.stage.registers_to_shared_operand"), u64(TileBytes) * 16 + Slots),
+                                             Resources<TileBytes * Slots, 0, Slots>> {
+    static_assert(TileBytes % 1024 == 0, "128-byte swizzled tiles must be 1024-byte aligned");
+};
+
 template <class Elem>
 struct StoreRowGlobal : Obligation<mix_u64(fnv1a_64_cstr("axp.protocol.store.row_global"), Elem::id)> {};
 

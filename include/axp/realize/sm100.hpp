@@ -778,6 +778,85 @@ AXP_DEV void exp2_block16(const uint32_t (&v)[32], int o16, unsigned long long c
     }
 }
 
+// ----------------------------------------------------------------------------
+// Leaves of the epilogue / softmax obligations (the device code the kernels call).
+// ----------------------------------------------------------------------------
+// ScalePromoteAccumulator: acc[i] = fma(s, partial[i], acc[i]) over the N partial sums a thread has read from tensor
+// memory; s is the product of the operand scales of this K block (the reference's scale hook,
+// include/axp/level3/gemm.hpp:104-116,1379-1382, applied to the fp32 partial sum instead of the operand tile).
+struct ScalePromoteFma {
+    template <int N>
+    AXP_DEV static void execute(float* acc, const uint32_t (&partial)[N], float s) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = fmaf(s, __uint_as_float(partial[i]), acc[i]);
+    }
+};
+
+// Fused epilogues on eight consecutive fp32 accumulator columns, ending in packed bf16:
+//   c_in != null : alpha * acc + beta * c_in as the reference's LinearCombinationVec evaluates it (MulAcc, MulC, Add:
+//                  three fp32 operations, no contraction; include/axp/level3/gemm.hpp:187-208,221-234);
+//   bias != null : act(acc + bias), act 0 = identity, 1 = SiLU x * sigmoid(x) with the Fast recipe's __expf
+//                  (BiasActivationVec, gemm.hpp:159-219; SiLU include/axp/realize/l0.hpp:1955-1965);
+//   neither      : plain cast.
+struct BiasActFma {
+    AXP_DEV static float activate(float x, float b, int act) {
+        x += b;
+        return act == 1 ? x / (1.0f + __expf(-x)) : x;
+    }
+    AXP_DEV static uint4 execute(const float (&f)[8], const float* bias, int act, const void* c_in = nullptr, float alpha = 1.0f,
+                                 float beta = 0.0f) {
+        float g[8];
+        if (c_in) {
+            const uint4 cv = *reinterpret_cast<const uint4*>(c_in);
+            const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float c0 = __uint_as_float(cw[i] << 16), c1 = __uint_as_float(cw[i] & 0xffff0000u);
+                g[2 * i] = __fadd_rn(__fmul_rn(alpha, f[2 * i]), __fmul_rn(beta, c0));
+                g[2 * i + 1] = __fadd_rn(__fmul_rn(alpha, f[2 * i + 1]), __fmul_rn(beta, c1));
+            }
+        } else if (bias) {
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias));
+            const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias) + 1);
+            g[0] = activate(f[0], b0.x, act);
+            g[1] = activate(f[1], b0.y, act);
+            g[2] = activate(f[2], b0.z, act);
+            g[3] = activate(f[3], b0.w, act);
+            g[4] = activate(f[4], b1.x, act);
+            g[5] = activate(f[5], b1.y, act);
+            g[6] = activate(f[6], b1.z, act);
+            g[7] = activate(f[7], b1.w, act);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) g[i] = f[i];
+        }
+        uint4 o;
+        o.x = PackBf16x2::execute(g[0], g[1]);
+        o.y = PackBf16x2::execute(g[2], g[3]);
+        o.z = PackBf16x2::execute(g[4], g[5]);
+        o.w = PackBf16x2::execute(g[6], g[7]);
+        return o;
+    }
+    // gated form: SiLU(gate) * up for two columns, packed
+    AXP_DEV static uint32_t gated(float g0, float g1, float u0, float u1) {
+        return PackBf16x2::execute(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+    }
+};
+
+// StoreRowGlobal: eight packed bf16 columns (16 bytes) of one output row.
+struct RowStoreVec16 {
+    AXP_DEV static void execute(void* dst, uint4 v) { *reinterpret_cast<uint4*>(dst) = v; }
+};
+
+// RowSoftmaxStateUpdate: sixteen softmax numerators of one row and their running sums (see exp2_block16).
+struct RowSoftmaxExp2 {
+    template <int kPolyMask>
+    AXP_DEV static void execute(const uint32_t (&v)[32], int o16, unsigned long long c2, unsigned long long neg2,
+                                unsigned long long& sum_a, unsigned long long& sum_b, float (&e)[16]) {
+        exp2_block16<kPolyMask>(v, o16, c2, neg2, sum_a, sum_b, e);
+    }
+};
+
 #endif  // __CUDACC__
 
 }  // namespace axp::realize::sm100

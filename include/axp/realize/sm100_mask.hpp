@@ -31,4 +31,10 @@ AXP_HD int causal_kv_tiles(long long q_base, int tile_m, int tile_n, long long s
     return int(last / tile_n) + 1;
 }
 
+// CausalMaskPredicate leaf: the element predicate and the whole-tile skip test.
+struct CausalMaskPred {
+    AXP_HD static bool execute(long long q, long long k) { return causal_valid(q, k); }
+    AXP_HD static bool skip(long long q_base, long long k_base, int tile_m) { return causal_tile_skip(q_base, k_base, tile_m); }
+};
+
 }  // namespace axp::realize::sm100

@@ -205,11 +205,14 @@ struct Obligation {
     using resources = Res;
 };
 
-// Base of every realization (reference core:3290-3300).
+// Base of every realization (reference core:3290-3300): the id mixes the obligation's id with the implementation id,
+// so that one implementation name registered for two obligations yields two realization ids.
 template <class ObligationT, iro::util::u64 ImplId>
 struct Realization {
     using obligation = ObligationT;
-    static constexpr iro::util::u64 id = ImplId;
+    static constexpr iro::util::u64 impl_id = ImplId;
+    static constexpr iro::util::u64 id =
+        iro::util::mix_u64(iro::util::fnv1a_64_cstr("iro.contract.Realization"), iro::util::mix_u64(ObligationT::id, ImplId));
 };
 
 }  // namespace iro::contract

@@ -39,6 +39,7 @@
 #include "axp/realize/sm100.hpp"
 #include "axp/realize/sm100_mask.hpp"
 #include "host_common.hpp"
+#include "kernel_config.hpp"
 
 namespace rz = axp::realize::sm100;
 
@@ -82,6 +83,16 @@ struct AttnCfg {
     static_assert(kN == 128 || (kN == 64 && !kFp8 && !kPSmem), "64-key tiles are realised for bf16 with P in tensor memory");
     static_assert(kSmem <= 227 * 1024, "shared memory budget");
 };
+
+// the default dispatch (launch_attn) and the configuration header agree
+namespace cfg = axp_shim::cfg;
+using DefaultCfgBf16 = AttnCfg<false, cfg::kAttnBf16.p_through_smem, cfg::kAttnBf16.kv_tile>;
+using DefaultCfgFp8 = AttnCfg<true, cfg::kAttnFp8.p_through_smem, cfg::kAttnFp8.kv_tile>;
+static_assert(cfg::kAttnBf16.kv_tile == kDefaultKvTileBf16 && cfg::kAttnFp8.p_through_smem == kDefaultPSmemFp8);
+static_assert(cfg::kAttnBf16.kv_stages == DefaultCfgBf16::kKvStages && cfg::kAttnBf16.dyn_smem == DefaultCfgBf16::kSmem);
+static_assert(cfg::kAttnFp8.kv_stages == DefaultCfgFp8::kKvStages && cfg::kAttnFp8.dyn_smem == DefaultCfgFp8::kSmem);
+static_assert(cfg::kAttnBf16.threads == kAttnThreads && cfg::kAttnFp8.threads == kAttnThreads && cfg::kAttnBf16.q_tiles == kQTiles &&
+              cfg::kAttnBf16.tile_q == kTileM && cfg::kAttnBf16.head_dim == kHeadDim);
 
 struct AttnParams {
     void* O;               // bf16 [BH, S, D]
@@ -189,6 +200,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // setmaxnreg only moves registers inside the CTA's launch allocation
     constexpr int kLaunchRegs = (65536 / kAttnThreads) / 8 * 8;      // 168
     constexpr int kProducerRegs = 56, kSoftmaxRegs = 224;
+    static_assert(kProducerRegs == cfg::kAttnBf16.producer_regs && kSoftmaxRegs == cfg::kAttnBf16.softmax_regs &&
+                  kProducerRegs == cfg::kAttnFp8.producer_regs && kSoftmaxRegs == cfg::kAttnFp8.softmax_regs);
     static_assert(128 * kProducerRegs + 256 * kSoftmaxRegs <= kAttnThreads * kLaunchRegs,
                   "register budgets exceed the CTA's launch allocation");
 
@@ -727,7 +740,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             uint32_t pk[32];
             auto block16 = [&](uint32_t (&v)[32], int o16, int b) {
                 float e[16];
-                rz::exp2_block16<kPolyMask>(v, o16, c2, neg2, sum_a, sum_b, e);
+                rz::RowSoftmaxExp2::execute<kPolyMask>(v, o16, c2, neg2, sum_a, sum_b, e);
                 if constexpr (kFp8 && kPSmem) {
                     uint32_t w[4];
 #pragma unroll

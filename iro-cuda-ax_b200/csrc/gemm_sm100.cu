@@ -30,6 +30,7 @@
 
 #include "axp/realize/sm100.hpp"
 #include "host_common.hpp"
+#include "kernel_config.hpp"
 
 namespace rz = axp::realize::sm100;
 
@@ -57,6 +58,15 @@ struct StageCfg {
     static constexpr int kStages = kCtaGroup == 1 ? 4 : 6;
     static constexpr int kDynSmem = kStages * kStageBytes + 1024;
 };
+
+// the default dispatch (launch_gemm) and the configuration header agree
+namespace cfg = axp_shim::cfg;
+static_assert(cfg::kGemmFp8.tile_m == kBM && cfg::kGemmFp8.tile_n == kBN && cfg::kGemmFp8.tile_k == kRowBytes);
+static_assert(cfg::kGemmBf16.tile_m == kBM && cfg::kGemmBf16.tile_n == kBN && cfg::kGemmBf16.tile_k * 2 == kRowBytes);
+static_assert(cfg::kGemmFp8.stages == StageCfg<cfg::kGemmFp8.cta_group>::kStages && cfg::kGemmFp8.stage_bytes == StageCfg<cfg::kGemmFp8.cta_group>::kStageBytes &&
+              cfg::kGemmFp8.dyn_smem == StageCfg<cfg::kGemmFp8.cta_group>::kDynSmem && cfg::kGemmFp8.tmem_cols == kTmemCols);
+static_assert(cfg::kGemmBf16.stages == StageCfg<cfg::kGemmBf16.cta_group>::kStages && cfg::kGemmBf16.stage_bytes == StageCfg<cfg::kGemmBf16.cta_group>::kStageBytes &&
+              cfg::kGemmBf16.dyn_smem == StageCfg<cfg::kGemmBf16.cta_group>::kDynSmem && cfg::kGemmBf16.tmem_cols == kTmemCols);
 
 struct GemmParams {
     const float* sA;      // [M, KB]
@@ -109,50 +119,8 @@ __device__ __forceinline__ void stamp(const GemmParams& p, int what, int n) {
 #endif
 }
 
-// Fused epilogue on the fp32 accumulator (reference epilogue::BiasActivationVec, include/axp/level3/gemm.hpp:
-// 159-219: Add(acc, bias) then the activation; SiLU(x) = x * sigmoid(x), include/axp/realize/l0.hpp:1955-1965,
-// with the Fast recipe's __expf).
-__device__ __forceinline__ float bias_act(float x, float b, int act) {
-    x += b;
-    return act == 1 ? x / (1.0f + __expf(-x)) : x;
-}
-// eight consecutive accumulator columns -> bias/activation (if any) -> packed bf16
-__device__ __forceinline__ uint4 finish8(const float (&f)[8], const float* bias, int act, const __nv_bfloat16* c_in = nullptr,
-                                         float alpha = 1.0f, float beta = 0.0f) {
-    float g[8];
-    if (c_in) {
-        // the reference's LinearCombinationVec: MulAcc, MulC, Add as three fp32 operations (no contraction)
-        const uint4 cv = *reinterpret_cast<const uint4*>(c_in);
-        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float c0 = __uint_as_float(cw[i] << 16), c1 = __uint_as_float(cw[i] & 0xffff0000u);
-            g[2 * i] = __fadd_rn(__fmul_rn(alpha, f[2 * i]), __fmul_rn(beta, c0));
-            g[2 * i + 1] = __fadd_rn(__fmul_rn(alpha, f[2 * i + 1]), __fmul_rn(beta, c1));
-        }
-    } else if (bias) {
-        const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias));
-        const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias) + 1);
-        g[0] = bias_act(f[0], b0.x, act);
-        g[1] = bias_act(f[1], b0.y, act);
-        g[2] = bias_act(f[2], b0.z, act);
-        g[3] = bias_act(f[3], b0.w, act);
-        g[4] = bias_act(f[4], b1.x, act);
-        g[5] = bias_act(f[5], b1.y, act);
-        g[6] = bias_act(f[6], b1.z, act);
-        g[7] = bias_act(f[7], b1.w, act);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) g[i] = f[i];
-    }
-    uint4 o;
-    o.x = rz::PackBf16x2::execute(g[0], g[1]);
-    o.y = rz::PackBf16x2::execute(g[2], g[3]);
-    o.z = rz::PackBf16x2::execute(g[4], g[5]);
-    o.w = rz::PackBf16x2::execute(g[6], g[7]);
-    return o;
-}
-
+// The fused epilogues (bias + activation, linear combination, gated) are the kit's BiasActFma leaf, the promotion of a
+// K-block partial its ScalePromoteFma leaf, the 16-byte row stores its RowStoreVec16 leaf (include/axp/realize/sm100.hpp).
 // Tile order: groups of kGroup row tiles sweep all column tiles, so that the CTAs
 // running at one time share a few A row panels and B column panels in L2.
 // Row tiles (of 128 rows) that share one sweep over the column tiles: the tiles the 148 CTAs work on at a time then touch
@@ -197,6 +165,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr int kEpilogueRegs = kEpiWG == 2 ? 232 : 112;
     static_assert(128 * kProducerRegs + 128 * kEpiWG * kEpilogueRegs <= kThreads * kLaunchRegs,
                   "register budgets exceed the CTA's launch allocation");
+    static_assert(kEpiWG != 2 || (kProducerRegs == cfg::kGemmFp8.producer_regs && kEpilogueRegs == cfg::kGemmFp8.epilogue_regs && kThreads == cfg::kGemmFp8.threads));
+    static_assert(kEpiWG != 4 || (kProducerRegs == cfg::kGemmBf16.producer_regs && kEpilogueRegs == cfg::kGemmBf16.epilogue_regs && kThreads == cfg::kGemmBf16.threads));
     constexpr int kElemsPerRow = kFp8 ? 128 : 64;     // K elements per stage
     constexpr int kMmaPerStage = kRowBytes / 32;      // one MMA consumes 32 bytes of K
     constexpr int kTileM = kBM * kCtaGroup;           // rows of the (pair) tile
@@ -435,9 +405,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     auto promote = [&](const uint32_t (&v)[32], int c) {
                         if (!(kProbes && (p.experiment & 1))) {
                             const float sc = (kGated && c >= kChunks / 2) ? s2 : s;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                accum[c * 32 + j] = fmaf(sc, __uint_as_float(v[j]), accum[c * 32 + j]);
+                            rz::ScalePromoteFma::execute(&accum[c * 32], v, sc);
                         }
                     };
                     if (!(kProbes && (p.experiment & 2))) {
@@ -474,9 +442,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                 for (int i = 0; i < 4; ++i) {
                                     const float g0 = accum[c * 8 + 2 * i], g1 = accum[c * 8 + 2 * i + 1];
                                     const float u0 = accum[kCols / 2 + c * 8 + 2 * i], u1 = accum[kCols / 2 + c * 8 + 2 * i + 1];
-                                    o[i] = rz::PackBf16x2::execute(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                                    o[i] = rz::BiasActFma::gated(g0, g1, u0, u1);
                                 }
-                                *reinterpret_cast<uint4*>(orow + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                                rz::RowStoreVec16::execute(orow + c * 8, make_uint4(o[0], o[1], o[2], o[3]));
                             }
                         }
                     }
@@ -487,9 +455,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             float f[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i) f[i] = accum[c * 8 + i];
-                            *reinterpret_cast<uint4*>(crow + c * 8) =
-                                finish8(f, p.bias ? p.bias + col0 + c * 8 : nullptr, p.act,
-                                        p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 8 : nullptr, p.alpha, p.beta);
+                            rz::RowStoreVec16::execute(crow + c * 8,
+                                rz::BiasActFma::execute(f, p.bias ? p.bias + col0 + c * 8 : nullptr, p.act,
+                                        p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 8 : nullptr, p.alpha, p.beta));
                         }
                     }
                 }
@@ -522,9 +490,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             for (int i = 0; i < 4; ++i) {
                                 const float g0 = __uint_as_float(vg[q * 8 + 2 * i]), g1 = __uint_as_float(vg[q * 8 + 2 * i + 1]);
                                 const float u0 = __uint_as_float(vu[q * 8 + 2 * i]), u1 = __uint_as_float(vu[q * 8 + 2 * i + 1]);
-                                o[i] = rz::PackBf16x2::execute(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                                o[i] = rz::BiasActFma::gated(g0, g1, u0, u1);
                             }
-                            *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                            rz::RowStoreVec16::execute(orow + q * 8, make_uint4(o[0], o[1], o[2], o[3]));
                         }
                     }
                 }
@@ -548,9 +516,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                 float f[8];
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[q * 8 + i]);
-                                *reinterpret_cast<uint4*>(crow + c * 32 + q * 8) =
-                                    finish8(f, p.bias ? p.bias + col0 + c * 32 + q * 8 : nullptr, p.act,
-                                            p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 32 + q * 8 : nullptr, p.alpha, p.beta);
+                                rz::RowStoreVec16::execute(crow + c * 32 + q * 8,
+                                    rz::BiasActFma::execute(f, p.bias ? p.bias + col0 + c * 32 + q * 8 : nullptr, p.act,
+                                            p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 32 + q * 8 : nullptr, p.alpha, p.beta));
                             }
                         }
                     }
@@ -732,8 +700,7 @@ gemm_fp8_n128_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                         __syncwarp();
                         if (lane == 0) rz::BarrierArrive::execute(&pipe.tmem_empty[acc]);
                     }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) accum[c * 16 + j] = fmaf(s, __uint_as_float(v[j]), accum[c * 16 + j]);
+                    rz::ScalePromoteFma::execute(&accum[c * 16], v, s);
                 }
                 if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
             }
@@ -745,9 +712,9 @@ gemm_fp8_n128_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                         float f[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) f[i] = accum[c * 8 + i];
-                        *reinterpret_cast<uint4*>(crow + c * 8) =
-                            finish8(f, p.bias ? p.bias + col0 + c * 8 : nullptr, p.act,
-                                    p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 8 : nullptr, p.alpha, p.beta);
+                        rz::RowStoreVec16::execute(crow + c * 8,
+                            rz::BiasActFma::execute(f, p.bias ? p.bias + col0 + c * 8 : nullptr, p.act,
+                                    p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 8 : nullptr, p.alpha, p.beta));
                     }
                 }
             }
@@ -806,8 +773,9 @@ int launch_gemm(const void* A, const void* B, const float* sA, const float* sB, 
     // 128 running sums of its row), BF16 = four.  (With a releasing remote arrive for the per-K-block accumulator
     // hand-over the FP8 pair was 45 % slower than single CTAs; with the relaxed arrive it is 3 % faster: 2115 against
     // 2053 TFLOP/s on 8192^3.)
-    const int epi_wg = (epi_wg_opt == 2 || epi_wg_opt == 4) ? epi_wg_opt : (kFp8 ? 2 : 4);
-    const int cta_group = (cta_group_opt == 1 || cta_group_opt == 2) ? cta_group_opt : 2;
+    constexpr cfg::Gemm kDefault = kFp8 ? cfg::kGemmFp8 : cfg::kGemmBf16;
+    const int epi_wg = (epi_wg_opt == 2 || epi_wg_opt == 4) ? epi_wg_opt : kDefault.threads / 128 - 1;
+    const int cta_group = (cta_group_opt == 1 || cta_group_opt == 2) ? cta_group_opt : kDefault.cta_group;
     const int b_box_div = cta_group;      // a CTA of a pair loads half of the tile's B rows
 
     const int64_t n_local = n_end - n_begin;

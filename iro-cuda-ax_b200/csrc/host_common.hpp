@@ -11,6 +11,7 @@
 #include <cstdint>
 #include <cstdio>
 
+#include "axp/realize/sm100_host.hpp"
 #include "axp_sm100.h"
 
 namespace axp_shim {
@@ -35,44 +36,15 @@ inline int fail(int code, const char* fmt, ...) {
             return ::axp_shim::fail(AXP_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
     } while (0)
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
 // Tiled tensor map of rank `rank` (dims/strides innermost first; strides in
-// bytes for dims 1..rank-1), 128-byte swizzle, zero fill outside the tensor.
-// The realization-level contract is HostMakeTensorMap
-// (reference include/axp/protocol/tma/contracts.hpp:71-93).
+// bytes for dims 1..rank-1), 128-byte swizzle, zero fill outside the tensor: the
+// kit's HostMakeTensorMap leaf with the shim's error convention.
 inline int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
                            const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                            CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return fail(AXP_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-    cuuint64_t d[5];
-    cuuint64_t s[5];
-    cuuint32_t b[5];
-    cuuint32_t es[5];
-    for (int i = 0; i < rank; ++i) {
-        d[i] = dims[i];
-        b[i] = box[i];
-        es[i] = 1;
-    }
-    for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
-    CUresult r = fn(out, dtype, cuuint32_t(rank), const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(AXP_ERR_CUDA, "cuTensorMapEncodeTiled returned %d", int(r));
+    const int r = axp::realize::sm100::HostTensorMapEncoder::execute(out, dtype, rank, base, dims, strides_bytes, box, swizzle);
+    if (r == -1) return fail(AXP_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    if (r != 0) return fail(AXP_ERR_CUDA, "cuTensorMapEncodeTiled returned %d", r);
     return AXP_OK;
 }
 

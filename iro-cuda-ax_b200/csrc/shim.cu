@@ -6,25 +6,37 @@
 #include "axp/realize/sm100.hpp"
 #include "axp/realize/sm100_mask.hpp"
 #include "host_common.hpp"
+#include "kernel_config.hpp"
 
 namespace rz = axp::realize::sm100;
 
 namespace {
+
+namespace cfg = axp_shim::cfg;
 
 struct Row {
     const char* key;
     axp_sm100_caps caps;
 };
 
-// One entry per row of manifests/kernels_sm100.json (same realization_key strings).
+constexpr axp_sm100_caps gemm_caps(int family, int elem_bits, const cfg::Gemm& g) {
+    return {0, family, elem_bits, g.tile_m, g.tile_n, g.tile_k, g.cta_group, g.stages, g.dyn_smem, g.tmem_cols, g.threads};
+}
+constexpr axp_sm100_caps attn_caps(int elem_bits, const cfg::Attn& a) {
+    // tile_n is the number of keys a step of the kernel takes (the KV tile of the shared-memory ring)
+    return {0, 2, elem_bits, a.tile_q, a.kv_tile, a.head_dim, 1, a.kv_stages, a.dyn_smem, a.tmem_cols, a.threads};
+}
+
+// One entry per row of manifests/kernels_sm100.json (same realization_key strings), filled from the configuration
+// the kernel translation units are checked against.
 const Row kRows[] = {
-    {"preset.gemm.fp8bs.128x256x128", {0, 1, 8, 128, 256, 128, 1, 4, 4 * 49152 + 1024, 512, 384}},
-    {"preset.gemm.bf16.128x256x64", {0, 1, 16, 128, 256, 64, 2, 6, 6 * 32768 + 1024, 512, 640}},
-    {"preset.gemm_fused.bf16.128x256x64.bias_silu", {0, 3, 16, 128, 256, 64, 2, 6, 6 * 32768 + 1024, 512, 640}},
-    {"preset.gemm_fused.bf16.128x256x64.lincomb", {0, 3, 16, 128, 256, 64, 2, 6, 6 * 32768 + 1024, 512, 640}},
-    {"preset.gemm_fused.bf16.128x256x64.swiglu", {0, 3, 16, 128, 256, 64, 2, 6, 6 * 32768 + 1024, 512, 640}},
-    {"preset.attention.bf16.128x128x128.causal", {0, 2, 16, 128, 128, 128, 1, 2, 6 * 32768 + 1024, 512, 384}},
-    {"preset.attention.fp8.gqa.128x128x128.causal", {0, 2, 8, 128, 128, 128, 1, 4, 10 * 16384 + 1024, 512, 384}},
+    {"preset.gemm.fp8bs.128x256x128", gemm_caps(1, 8, cfg::kGemmFp8)},
+    {"preset.gemm.bf16.128x256x64", gemm_caps(1, 16, cfg::kGemmBf16)},
+    {"preset.gemm_fused.bf16.128x256x64.bias_silu", gemm_caps(3, 16, cfg::kGemmBf16)},
+    {"preset.gemm_fused.bf16.128x256x64.lincomb", gemm_caps(3, 16, cfg::kGemmBf16)},
+    {"preset.gemm_fused.bf16.128x256x64.swiglu", gemm_caps(3, 16, cfg::kGemmBf16)},
+    {"preset.attention.bf16.128x128x128.causal", attn_caps(16, cfg::kAttnBf16)},
+    {"preset.attention.fp8.gqa.128x128x128.causal", attn_caps(8, cfg::kAttnFp8)},
 };
 
 __global__ void causal_mask_tile_kernel(long long q_base, long long k_base, int tile_m, int tile_n,

@@ -12,6 +12,8 @@
 #endif
 #include <axp/l4/resolve.hpp>
 
+#include "../../iro-cuda-ax_b200/csrc/kernel_config.hpp"   // the configuration the kernel translation units are checked against
+
 namespace {
 
 using iro::util::fnv1a_64_cstr;
@@ -82,8 +84,44 @@ using GBf16 = Graph<preset::GemmBf16_128x256x64>;
 using GAttn = Graph<preset::Attention128x128x128CausalBf16>;
 using GAttn8 = Graph<preset::Attention128x128x128CausalFp8Gqa>;
 static_assert(GFp8::scaled && !GBf16::scaled);
-static_assert(GFp8::smem_bytes == 4 * (128 * 128 + 256 * 128) && GFp8::tmem_cols == 512 && GFp8::mma_per_stage == 4);
+static_assert(GFp8::smem_bytes == 6 * (128 * 128 + 128 * 128) && GFp8::tmem_cols == 512 && GFp8::mma_per_stage == 4);
 static_assert(GBf16::smem_bytes == 6 * (128 * 128 + 128 * 128) && GBf16::mma_per_stage == 4 && GBf16::threads == 640);
+
+// ---- the graphs describe the kernels the default dispatch launches ---------------------
+namespace cfg = axp_shim::cfg;
+template <class G>
+constexpr bool gemm_graph_matches(const cfg::Gemm& k) {
+    return G::block_m == k.tile_m && G::block_n == k.tile_n && G::block_k == k.tile_k && G::cta_group == k.cta_group && G::stages == k.stages &&
+           G::smem_bytes == k.stages * k.stage_bytes && G::smem_bytes + 1024 == k.dyn_smem && G::tmem_cols == k.tmem_cols &&
+           G::threads == k.threads && G::producer_regs == k.producer_regs && G::epilogue_regs == k.epilogue_regs;
+}
+template <class G>
+constexpr bool attention_graph_matches(const cfg::Attn& k) {
+    return G::tile_q == k.tile_q && G::kv_step == k.kv_tile && G::head_dim == k.head_dim && G::q_tiles == k.q_tiles && G::stages == k.kv_stages &&
+           G::smem_bytes + 1024 == k.dyn_smem && G::tmem_cols == k.tmem_cols && G::threads == k.threads && G::producer_regs == k.producer_regs &&
+           G::softmax_regs == k.softmax_regs && G::issuers == k.issuers && G::p_through_smem == k.p_through_smem;
+}
+static_assert(gemm_graph_matches<GFp8>(cfg::kGemmFp8), "level-3 graph of the FP8 GEMM row and the launched kernel differ");
+static_assert(gemm_graph_matches<GBf16>(cfg::kGemmBf16), "level-3 graph of the bf16 GEMM row and the launched kernel differ");
+static_assert(gemm_graph_matches<Graph<preset::GemmBf16_128x256x64BiasSiLU>>(cfg::kGemmBf16));
+static_assert(attention_graph_matches<GAttn>(cfg::kAttnBf16), "level-3 graph of the bf16 attention row and the launched kernel differ");
+static_assert(attention_graph_matches<GAttn8>(cfg::kAttnFp8), "level-3 graph of the E4M3 attention row and the launched kernel differ");
+
+// ---- intent selectors (include/axp/kits/intent.hpp) -----------------------------------------
+namespace kd = axp::kit::detail;
+namespace mp = axp::intent::memory_pattern;
+namespace lm = axp::intent::load_mode;
+static_assert(std::is_same_v<kd::select_swizzle_t<mp::Optimized, iro::elem::e4m3, 128, Cap, true>, axp::swizzle::B128>);
+static_assert(std::is_same_v<kd::select_swizzle_t<mp::Optimized, iro::elem::bf16, 64, Cap, false>, axp::swizzle::B128>);
+static_assert(std::is_same_v<kd::select_swizzle_t<mp::Optimized, iro::elem::bf16, 32, Cap, true>, axp::swizzle::B64>);
+static_assert(std::is_same_v<kd::select_swizzle_t<mp::Optimized, iro::elem::e4m3, 32, Cap, true>, axp::swizzle::B32>);
+static_assert(std::is_same_v<kd::select_swizzle_t<mp::Optimized, iro::elem::e4m3, 16, Cap, true>, axp::swizzle::None>);
+static_assert(std::is_same_v<kd::select_swizzle_t<mp::None, iro::elem::bf16, 64, Cap, true>, axp::swizzle::None>);
+static_assert(kd::is_tma_config_v<kd::select_tma_t<lm::AsyncPrefetch, Cap, void, preset::GemmA, axp::level3::gemm_pipe_tag>>);
+static_assert(std::is_same_v<kd::select_tma_t<lm::Streaming, Cap, void, preset::GemmA, axp::level3::gemm_pipe_tag>, kd::streaming_tag>);
+static_assert(std::is_same_v<kd::select_schedule_t<axp::intent::schedule::ProducerConsumer, Cap>, axp::intent::schedule::ProducerConsumer>);
+static_assert(std::is_same_v<GFp8::a_swizzle, axp::swizzle::B128> && std::is_same_v<GAttn::q_swizzle, axp::swizzle::B128>);
+static_assert(axp::swizzle::B128::tensor_map_swizzle == 3 && axp::swizzle::B128::descriptor_code == 2);
 static_assert(iro::util::contains<px::ScalePromoteAccumulator<axp::recipe::E4M3BlockScaledAccF32OutBF16>, GFp8::obligations>::value);
 static_assert(!iro::util::contains<px::ScalePromoteAccumulator<axp::recipe::E4M3BlockScaledAccF32OutBF16>, GBf16::obligations>::value);
 using GFused = Graph<preset::GemmBf16_128x256x64BiasSiLU>;
@@ -96,15 +134,27 @@ static_assert(GLin::id != GFused::id);
 using GSwi = Graph<preset::GemmBf16_128x256x64SwiGLU>;
 static_assert(iro::util::contains<px::GatedActivation<preset::GemmUpOperand, axp::level3::epilogue::act::SiLU>, GSwi::obligations>::value);
 static_assert(GSwi::id != GFused::id);
-static_assert(GAttn::is_causal && GAttn::tmem_cols == 512 && GAttn::smem_bytes == (2 + 2 * 2) * 32768);
-static_assert(GAttn8::smem_bytes == (2 + 2 * 4) * 16384);
+static_assert(GAttn::is_causal && GAttn::tmem_cols == 512 && GAttn::smem_bytes == 2 * 32768 + 2 * 4 * 16384);
+static_assert(GAttn8::smem_bytes == (2 + 4 + 2 * 3) * 16384);      // Q tiles, P tiles, K / V stages
 static_assert(GFp8::id != GBf16::id && GAttn::id != GAttn8::id, "distinct obligation lists hash differently");
 
 // ---- kit binding --------------------------------------------------------------------
 using MmaFp8 = px::Tcgen05Mma<128, 256, 32, iro::elem::e4m3, iro::elem::e4m3, 1>;
 static_assert(axp::kit::sm100::bind<MmaFp8>::found);
 static_assert(std::is_same_v<axp::kit::sm100::bind<MmaFp8>::realization::obligation, MmaFp8>);
-static_assert(axp::kit::sm100::bind<MmaFp8>::realization::id == fnv1a_64_cstr("axp.realize.sm100.compute.tcgen05_mma_ss"));
+static_assert(axp::kit::sm100::bind<MmaFp8>::realization::impl_id == fnv1a_64_cstr("axp.realize.sm100.compute.tcgen05_mma_ss"));
+// the realization id mixes obligation and implementation (reference include/iro_cuda_ax_core.hpp:3290-3300)
+static_assert(axp::kit::sm100::bind<MmaFp8>::realization::id ==
+              iro::util::mix_u64(fnv1a_64_cstr("iro.contract.Realization"),
+                                 iro::util::mix_u64(MmaFp8::id, fnv1a_64_cstr("axp.realize.sm100.compute.tcgen05_mma_ss"))));
+// every leaf of every bound realization carries an execute member (the kernels call these)
+static_assert(axp::kit::sm100::binds_all<GFp8::obligations>::value && axp::kit::sm100::binds_all<GAttn8::obligations>::value);
+static_assert(axp::kit::sm100::detail::has_execute<axp::realize::sm100::ScalePromoteFma>::value &&
+              axp::kit::sm100::detail::has_execute<axp::realize::sm100::TmemLoadWait>::value &&
+              axp::kit::sm100::detail::has_execute<axp::realize::sm100::HostTensorMapEncoder>::value &&
+              axp::kit::sm100::detail::has_execute<axp::realize::sm100::CausalMaskPred>::value);
+struct NoExecuteProbe {};
+static_assert(!axp::kit::sm100::detail::has_execute<NoExecuteProbe>::value);
 static_assert(iro::util::contains<axp::realize::sm100::Tcgen05Mma<1, false>, axp::kit::sm100::bind<MmaFp8>::realization::leaves>::value);
 static_assert(axp::kit::sm100::bind<px::BoundedBarrierWait>::found);
 
