@@ -1,5 +1,7 @@
 // Intent vocabulary of the L4 patterns: portable wishes, no mechanism.
 // Same names as the reference (include/axp/intent.hpp:7-31).
+// Public surface restated from tribe-iro/iro-cuda-ax (MIT licence, Copyright (c) 2026 IRO; the notice is kept in
+// THIRD_PARTY_NOTICES.md at the repository root).
 #pragma once
 #include <iro_cuda_ax_core.hpp>
 

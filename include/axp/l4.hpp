@@ -1,5 +1,7 @@
 // L4 intent patterns: portable descriptions only (reference include/axp/l4.hpp:18-74,
 // same parameter lists and defaults), plus the canonical presets.
+// Public surface restated from tribe-iro/iro-cuda-ax (MIT licence, Copyright (c) 2026 IRO; the notice is kept in
+// THIRD_PARTY_NOTICES.md at the repository root).
 #pragma once
 #include <iro_cuda_ax_core.hpp>
 

@@ -1,6 +1,8 @@
 // Profiles and the bind key (reference include/axp/l4/bind_key.hpp:11-38): the same
 // mixing order, so that a key computed here equals the reference's for the same
 // (graph_hash, capability, profile, realization_key).
+// Public surface restated from tribe-iro/iro-cuda-ax (MIT licence, Copyright (c) 2026 IRO; the notice is kept in
+// THIRD_PARTY_NOTICES.md at the repository root).
 #pragma once
 
 #if !defined(AXP_LIBRARY_BUILD)

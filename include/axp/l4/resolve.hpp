@@ -1,5 +1,7 @@
 // (graph_hash, capability, profile) -> manifest row -> realization key and bind key
 // (reference include/axp/l4/resolve.hpp:29-61, same checks in the same order).
+// Public surface restated from tribe-iro/iro-cuda-ax (MIT licence, Copyright (c) 2026 IRO; the notice is kept in
+// THIRD_PARTY_NOTICES.md at the repository root).
 #pragma once
 
 #if !defined(AXP_LIBRARY_BUILD)

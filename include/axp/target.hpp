@@ -1,6 +1,8 @@
 // Compile-time target capability (reference include/axp/target.hpp:7-38): device
 // passes use __CUDA_ARCH__, host passes need AXP_TARGET_SM; sm100 additionally
 // needs AXP_ENABLE_SM100.  Only the sm90 and sm100 lanes exist in this tree.
+// Public surface restated from tribe-iro/iro-cuda-ax (MIT licence, Copyright (c) 2026 IRO; the notice is kept in
+// THIRD_PARTY_NOTICES.md at the repository root).
 #pragma once
 #include <iro_cuda_ax_core.hpp>
 

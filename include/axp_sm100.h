@@ -250,9 +250,9 @@ int axp_sm100_selftest_bounded_wait(int64_t limit_cycles, void* stream, uint32_t
 
 /* Process-wide tuning option; value 0 restores the library default.
  *   "gemm.epilogue_warpgroups"  2 or 4: warpgroups that drain the accumulator
- *   "gemm.cta_group"            1 or 2: CTAs cooperating on one MMA (2 = cluster pair,
- *                               256 x 256 tile, each CTA loads its own operand halves)
- *   "gemm.fp8_tile"             FP8 block-scaled GEMM: 256 = 128 x 256 tiles, one CTA per SM (default); 128 = 128 x 128
+ *   "gemm.cta_group"            1 or 2: CTAs cooperating on one MMA (2 = cluster pair, the default for both GEMMs:
+ *                               256 x 256 tile per pair, each CTA loads its own operand halves)
+ *   "gemm.fp8_tile"             FP8 block-scaled GEMM: 256 = 128 x 256 tiles per CTA (default); 128 = 128 x 128
  *                               tiles with two CTAs per SM (same results bit for bit; measured 13 % slower on 8192^3)
  *   "attn.exp_mode"             how the softmax exponentials are evaluated: 1 = all on the SFU;
  *                               2 / 3 / 4 = 2 / 4 / 3 of every 8 pairs as a polynomial on the FMA pipe
@@ -263,6 +263,9 @@ int axp_sm100_selftest_bounded_wait(int64_t limit_cycles, void* stream, uint32_t
  *   "attn.issuers"              1 or 2 threads issuing the attention MMAs (2: one per Q tile)
  *   "attn.decode_kernel"        split-KV calls with at most 16 query rows per KV head: 1 = the forward kernel,
  *                               2 = the decode kernel with swapped operands (keys on the tensor-memory lanes)
+ * Two more names, "debug_buffer" and "gemm.experiment", belong to the latency probes of builds made with
+ * -DAXP_SM100_LATENCY_PROBES (globaltimer stamps, parts of the epilogue switched off; results are then not
+ * valid); the production library answers AXP_ERR_UNSUPPORTED for them and its kernels carry none of that code.
  * The counterpart upstream is the expert override traits of the intent selectors
  * (include/axp/kits/intent.hpp:108-125), which are compile-time. */
 int axp_sm100_set_option(const char* name, int64_t value);

@@ -112,8 +112,10 @@ struct AttnParams {
     int num_heads;         // (batch, head) pairs of this launch; grid.x = num_q_blocks * num_heads
     float scale;           // softmax scale
     uint32_t* status;
-    unsigned long long* debug;   // optional timestamp buffer for latency experiments (null in production)
-    int experiment;              // latency experiments only; 0 in production
+#if defined(AXP_SM100_LATENCY_PROBES)
+    unsigned long long* debug;   // timestamp buffer of the latency experiments
+    int experiment;              // bits 8..: the CTA that is timed
+#endif
     // split-KV: CTA z of gridDim.z visits KV tiles [z * tiles_per_split, (z + 1) * tiles_per_split) and, when
     // splits > 1, leaves its unnormalised accumulator (fp32) and (m * c, l) per row in scratch memory
     int splits;
@@ -443,12 +445,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     if (ok && j + kSBufs < n) ok = qk_step(j + kSBufs);
                 }
             }
-            if constexpr (kAttnProbes) {
-                if (leader && p.debug && blockIdx.x == unsigned(p.experiment >> 8)) {
-                    for (int i = 0; i < 4; ++i) p.debug[15 * 32 + 8 + qt * 5 + i] = (unsigned long long)dbg_w[i];
-                    p.debug[15 * 32 + 8 + qt * 5 + 4] = (unsigned long long)(clock64() - dbg_start);
-                }
+#if defined(AXP_SM100_LATENCY_PROBES)
+            if (leader && p.debug && blockIdx.x == unsigned(p.experiment >> 8)) {
+                for (int i = 0; i < 4; ++i) p.debug[15 * 32 + 8 + qt * 5 + i] = (unsigned long long)dbg_w[i];
+                p.debug[15 * 32 + 8 + qt * 5 + 4] = (unsigned long long)(clock64() - dbg_start);
             }
+#endif
             // KV tiles only the other Q tile visits: K_j then V_j in tile order, as the producer refills them
             for (int j = n; j < n_max && ok; ++j) {
                 if (!(ok = wait_or_report(&pipe.k_full[kst], kphase, rz::kBarFull))) break;
@@ -788,13 +790,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if constexpr (kAttnProbes) { const long long t = clock64(); dbg_ph[3] += t - dbg_t0; dbg_t0 = t; }
             if (lane == 0 && quarter == 0) attn_stamp(p, qt * 5 + 4, j);     // P handed to the issuer
         }
-        if constexpr (kAttnProbes) {
-            if (lane == 0 && quarter == 0 && p.debug && blockIdx.x == unsigned(p.experiment >> 8)) {
-                p.debug[15 * 32 + qt * 2 + 0] = (unsigned long long)dbg_wait;                 // cycles waiting for S, steps 1..n-1
-                p.debug[15 * 32 + qt * 2 + 1] = (unsigned long long)(clock64() - dbg_first);  // cycles from first S to loop end
-                for (int i = 0; i < 4; ++i) p.debug[15 * 32 + 20 + qt * 4 + i] = (unsigned long long)dbg_ph[i];
-            }
+#if defined(AXP_SM100_LATENCY_PROBES)
+        if (lane == 0 && quarter == 0 && p.debug && blockIdx.x == unsigned(p.experiment >> 8)) {
+            p.debug[15 * 32 + qt * 2 + 0] = (unsigned long long)dbg_wait;                 // cycles waiting for S, steps 1..n-1
+            p.debug[15 * 32 + qt * 2 + 1] = (unsigned long long)(clock64() - dbg_first);  // cycles from first S to loop end
+            for (int i = 0; i < 4; ++i) p.debug[15 * 32 + 20 + qt * 4 + i] = (unsigned long long)dbg_ph[i];
         }
+#endif
         if (lane == 0 && quarter == 0) attn_stamp(p, 14, 2 + qt * 3);       // softmax loop left
         if (ok && n > 0) {
             ok = __all_sync(0xffffffffu, rz::BarrierWait::execute(&pipe.o_done[qt][(n - 1) & 1], uint32_t(((n - 1) >> 1) & 1), abort_flag));
@@ -1514,8 +1516,10 @@ int launch_attn(const void* Q, const void* K, const void* V, const float* dq, co
     p.num_q_blocks = int((Sq + kQTiles * kTileM - 1) / (kQTiles * kTileM));
     p.scale = scale;
     p.status = status_dev;
+#if defined(AXP_SM100_LATENCY_PROBES)
     p.debug = reinterpret_cast<unsigned long long*>(debug_pointer().load(std::memory_order_relaxed));
     p.experiment = option_slot(kOptGemmExperiment).load(std::memory_order_relaxed);
+#endif
     // tuning option "attn.issuers": 0 = library default, 1 or 2 MMA-issuing threads
     const int iss_opt = option_slot(kOptAttnIssuers).load(std::memory_order_relaxed);
     p.two_issuers = (iss_opt == 1 || iss_opt == 2) ? int(iss_opt == 2) : 1;   // measured with two: bf16 +12 %, E4M3 +4 %

@@ -44,11 +44,6 @@ constexpr int kTmemCols = 512;
 constexpr int kAccCols = kBN;                  // columns per accumulator stage
 constexpr int kMaxStages = 6;
 constexpr int kDefaultFp8TileN = 256;
-#if defined(AXP_SM100_LATENCY_PROBES)
-constexpr bool kProbes = true;     // timing experiments may switch parts of the epilogue off
-#else
-constexpr bool kProbes = false;
-#endif
 
 template <int kCtaGroup>
 struct StageCfg {
@@ -86,9 +81,19 @@ struct GemmParams {
     float beta;
     long long ldc;
     uint32_t* status;
-    unsigned long long* debug;   // optional timestamp buffer for latency experiments (null in production)
-    int experiment;       // timing experiments only (bit 0: skip the promotion arithmetic); 0 in production
+#if defined(AXP_SM100_LATENCY_PROBES)
+    unsigned long long* debug;   // timestamp buffer of the latency experiments
+    int experiment;       // bit 0: skip the promotion arithmetic, bit 1: skip the tensor-memory reads (results invalid; times only)
+#endif
 };
+
+// Parts of the epilogue can be switched off in builds with -DAXP_SM100_LATENCY_PROBES only; the production kernels and
+// their parameter block carry none of it.
+#if defined(AXP_SM100_LATENCY_PROBES)
+#define AXP_GEMM_EXPERIMENT(p, mask) (((p).experiment & (mask)) != 0)
+#else
+#define AXP_GEMM_EXPERIMENT(p, mask) false
+#endif
 
 struct Pipe {
     uint64_t full[kMaxStages];
@@ -403,12 +408,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     // issuer as soon as the last read has landed, before the last chunk's FMAs
                     uint32_t va[32], vb[32];
                     auto promote = [&](const uint32_t (&v)[32], int c) {
-                        if (!(kProbes && (p.experiment & 1))) {
+                        if (!AXP_GEMM_EXPERIMENT(p, 1)) {
                             const float sc = (kGated && c >= kChunks / 2) ? s2 : s;
                             rz::ScalePromoteFma::execute(&accum[c * 32], v, sc);
                         }
                     };
-                    if (!(kProbes && (p.experiment & 2))) {
+                    if (!AXP_GEMM_EXPERIMENT(p, 2)) {
                         rz::TmemLoad32x32::execute(chunk_addr(0), va);
                         rz::TmemLoadWait::execute(va);
 #pragma unroll
@@ -426,7 +431,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     rz::Tcgen05FenceBefore::execute();
                     __syncwarp();
                     if (lane == 0) release_acc(&pipe.tmem_empty[acc]);
-                    if (!(kProbes && (p.experiment & 2))) promote(vb, kChunks - 1);
+                    if (!AXP_GEMM_EXPERIMENT(p, 2)) promote(vb, kChunks - 1);
                     if (lane == 0) stamp(p, 3, n_dbg);   // this warp's release issued
                     ++n_dbg;
                     if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -812,8 +817,10 @@ int launch_gemm(const void* A, const void* B, const float* sA, const float* sB, 
     p.beta = beta;
     p.ldc = ldc;
     p.status = status_dev;
+#if defined(AXP_SM100_LATENCY_PROBES)
     p.debug = reinterpret_cast<unsigned long long*>(axp_shim::debug_pointer().load(std::memory_order_relaxed));
     p.experiment = axp_shim::option_slot(axp_shim::kOptGemmExperiment).load(std::memory_order_relaxed);
+#endif
 
     const int64_t tile_m = kBM * cta_group;
     const int64_t tiles = ((M + tile_m - 1) / tile_m) * ((n_local + kBN - 1) / kBN);

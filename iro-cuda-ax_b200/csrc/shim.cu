@@ -84,9 +84,16 @@ std::atomic<long long>& axp_shim::debug_pointer() {
 
 extern "C" int axp_sm100_set_option(const char* name, int64_t value) {
     if (!name) return axp_shim::fail(AXP_ERR_BAD_ARG, "set_option: name is null");
-    if (!strcmp(name, "debug_buffer")) {   // device pointer to 512 uint64 timestamps (latency experiments), or 0
-        axp_shim::debug_pointer().store((long long)value);
+    if (!strcmp(name, "debug_buffer") || !strcmp(name, "gemm.experiment")) {
+#if defined(AXP_SM100_LATENCY_PROBES)
+        // "debug_buffer": device pointer to 512 uint64 timestamps, or 0; "gemm.experiment": parts of the kernels switched off
+        // (results are not valid when non-zero)
+        if (!strcmp(name, "debug_buffer")) axp_shim::debug_pointer().store((long long)value);
+        else axp_shim::option_slot(axp_shim::kOptGemmExperiment).store(int(value));
         return AXP_OK;
+#else
+        return axp_shim::fail(AXP_ERR_UNSUPPORTED, "set_option: '%s' exists only in builds with -DAXP_SM100_LATENCY_PROBES", name);
+#endif
     }
     if (!strcmp(name, "gemm.epilogue_warpgroups")) {
         if (value != 0 && value != 2 && value != 4) return axp_shim::fail(AXP_ERR_BAD_ARG, "gemm.epilogue_warpgroups must be 0, 2 or 4");
@@ -101,10 +108,6 @@ extern "C" int axp_sm100_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "gemm.fp8_tile")) {   // FP8 block-scaled GEMM: 0 default, 128 (128 x 128 tiles, two CTAs per SM) or 256
         if (value != 0 && value != 128 && value != 256) return axp_shim::fail(AXP_ERR_BAD_ARG, "gemm.fp8_tile must be 0, 128 or 256");
         axp_shim::option_slot(axp_shim::kOptGemmFp8Tile).store(int(value));
-        return AXP_OK;
-    }
-    if (!strcmp(name, "gemm.experiment")) {   // timing experiments; results are not valid when non-zero
-        axp_shim::option_slot(axp_shim::kOptGemmExperiment).store(int(value));
         return AXP_OK;
     }
     if (!strcmp(name, "attn.exp_mode")) {

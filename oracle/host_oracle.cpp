@@ -634,12 +634,31 @@ void oracle_attn_fwd_bf16_tile_recipe(const uint16_t* Q, const uint16_t* Kp, con
 // Any reference maximum gives the same softmax; fixing the rule fixes where P is
 // rounded to E4M3 (include/axp/detail/conversion.hpp:83-95 saturating policy), which
 // is what the <= 1e-2 parity bar compares.
+// `rescale_threshold` (log2 units) is the laziness of the reference maximum: 8 is the rule above; 0 is the STANDARD
+// online softmax, whose reference is the running maximum itself (advanced whenever a tile maximum exceeds it, so that
+// P <= 1 always).  The second form knows nothing of the kernel's schedule and is the independent check of the recipe.
+void oracle_attn_fwd_fp8_ex(const uint8_t* Q, const uint8_t* Kp, const uint8_t* V,
+                            const float* dq, const float* dk, const float* dv,
+                            uint16_t* O, float* LSE,
+                            int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                            float scale, int causal, int tile_n, float rescale_threshold,
+                            int64_t bh0, int64_t bh1, int64_t q0, int64_t q1);
+
 void oracle_attn_fwd_fp8(const uint8_t* Q, const uint8_t* Kp, const uint8_t* V,
                          const float* dq, const float* dk, const float* dv,
                          uint16_t* O, float* LSE,
                          int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
                          float scale, int causal, int tile_n,
                          int64_t bh0, int64_t bh1, int64_t q0, int64_t q1) {
+    oracle_attn_fwd_fp8_ex(Q, Kp, V, dq, dk, dv, O, LSE, B, Hq, Hkv, S, D, scale, causal, tile_n, 8.0f, bh0, bh1, q0, q1);
+}
+
+void oracle_attn_fwd_fp8_ex(const uint8_t* Q, const uint8_t* Kp, const uint8_t* V,
+                            const float* dq, const float* dk, const float* dv,
+                            uint16_t* O, float* LSE,
+                            int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                            float scale, int causal, int tile_n, float rescale_threshold,
+                            int64_t bh0, int64_t bh1, int64_t q0, int64_t q1) {
     (void)B;
     const int64_t grp = Hq / Hkv;
     const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
@@ -678,7 +697,7 @@ void oracle_attn_fwd_fp8(const uint8_t* Q, const uint8_t* Kp, const uint8_t* V,
                     }
                     if (k_base == 0) {
                         r = mx;
-                    } else if ((mx - r) * c > 8.0f) {
+                    } else if ((mx - r) * c > rescale_threshold) {
                         const float f = std::exp2((r - mx) * c);
                         r = mx;
                         l *= f;

@@ -287,8 +287,12 @@ def attn_fwd_bf16_tile_recipe(Q, K, V, scale: float, causal: bool, tile_m: int =
 
 
 def attn_fwd_fp8(Q, K, V, dq, dk, dv, scale: float, causal: bool, tile_n: int = 128,
-                 bh_range=None, q_range=None, out=None):
-    """Q [B,Hq,S,D], K/V [B,Hkv,S,D] E4M3 bytes; dq [B*Hq], dk/dv [B*Hkv] f32 descales."""
+                 bh_range=None, q_range=None, out=None, rescale_threshold: float = 8.0):
+    """Q [B,Hq,S,D], K/V [B,Hkv,S,D] E4M3 bytes; dq [B*Hq], dk/dv [B*Hkv] f32 descales.
+
+    ``rescale_threshold`` (log2 units): 8 = P taken against a reference maximum that is advanced lazily (the rule the
+    sm100 kernel follows); 0 = the standard online softmax with a per-tile running maximum (P <= 1), which knows
+    nothing of the kernel's schedule."""
     Q = np.ascontiguousarray(Q, dtype=np.uint8)
     K = np.ascontiguousarray(K, dtype=np.uint8)
     V = np.ascontiguousarray(V, dtype=np.uint8)
@@ -300,10 +304,10 @@ def attn_fwd_fp8(Q, K, V, dq, dk, dv, scale: float, causal: bool, tile_n: int = 
     O, LSE = out if out is not None else (np.zeros(Q.shape, np.uint16), np.zeros((B, Hq, S), np.float32))
     bh0, bh1 = bh_range or (0, B * Hq)
     q0, q1 = q_range or (0, S)
-    lib().oracle_attn_fwd_fp8(_p(Q), _p(K), _p(V), _p(dq), _p(dk), _p(dv), _p(O), _p(LSE),
-                              _i64(B), _i64(Hq), _i64(Hkv), _i64(S), _i64(D), ctypes.c_float(scale),
-                              ctypes.c_int(int(causal)), ctypes.c_int(tile_n),
-                              _i64(bh0), _i64(bh1), _i64(q0), _i64(q1))
+    lib().oracle_attn_fwd_fp8_ex(_p(Q), _p(K), _p(V), _p(dq), _p(dk), _p(dv), _p(O), _p(LSE),
+                                 _i64(B), _i64(Hq), _i64(Hkv), _i64(S), _i64(D), ctypes.c_float(scale),
+                                 ctypes.c_int(int(causal)), ctypes.c_int(tile_n), ctypes.c_float(rescale_threshold),
+                                 _i64(bh0), _i64(bh1), _i64(q0), _i64(q1))
     return O, LSE
 
 

@@ -142,6 +142,52 @@ def test_fp8_attention_full_size_sampled_heads(pkg, oracle, dev):
             assert np.abs(L[b, h, q0:q1].cpu().numpy() - Lw[0, 0, q0:q1]).max() <= 1e-3
 
 
+def _exact_fp8_attention_rows(oracle, q, k, v, dq, dk, dv, scale, q0, q1):
+    """float64 causal attention of one head on the dequantised operands, P NOT quantised: rows [q0, q1)."""
+    qf = oracle.e4m3_decode(q[0, 0, q0:q1]).astype(np.float64)
+    kf = oracle.e4m3_decode(k[0, 0]).astype(np.float64)
+    vf = oracle.e4m3_decode(v[0, 0]).astype(np.float64)
+    s = qf @ kf.T * (float(scale) * float(dq) * float(dk))
+    s = np.where(np.arange(kf.shape[0])[None, :] <= np.arange(q0, q1)[:, None], s, -np.inf)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    return (p @ vf) / p.sum(-1, keepdims=True) * float(dv)
+
+
+def test_fp8_attention_against_the_standard_online_softmax(pkg, oracle, dev):
+    """The E4M3 recipe rounds P to E4M3 before P.V, so WHERE P is taken (against which reference maximum) decides which
+    values are rounded.  The kernel advances its reference lazily; the parity oracle used elsewhere follows that rule.
+    This test holds the kernel against an oracle that does not know the kernel: the standard online softmax (per-tile
+    running maximum, P <= 1), and against exact float64 attention with unquantised P, on cfg4's shape (sampled heads
+    and rows) and on a small full problem.
+      (i)   GPU vs standard-recipe oracle: two roundings of different P values, i.e. twice the recipe's own rounding noise;
+      (ii)  GPU vs lazy-rule oracle: same rounding points, the <= 1e-2 bar;
+      (iii) GPU vs exact: must be no further from the truth than the standard recipe is (within 15 %)."""
+    B, Hq, Hkv, S, D = 4, 64, 8, 8192, 128
+    Q, K, V, dq, dk, dv, scale = pkg.synth.fp8_attention_inputs(B, Hq, Hkv, S, D, seed=0, device=dev)
+    O, _ = pkg.ops.attn_fwd_fp8(Q, K, V, dq, dk, dv, scale, True)
+    pkg.ops.check_status(dev)
+    worst = {"std": 0.0, "lazy": 0.0, "gpu_exact": 0.0, "std_exact": 0.0}
+    for bh in (3, 130, B * Hq - 2):
+        b, h = divmod(bh, Hq)
+        hk = h // (Hq // Hkv)
+        kv = b * Hkv + hk
+        q, k, v = u8(Q[b:b + 1, h:h + 1]), u8(K[b:b + 1, hk:hk + 1]), u8(V[b:b + 1, hk:hk + 1])
+        a, bb, c = dq[bh:bh + 1].cpu().numpy(), dk[kv:kv + 1].cpu().numpy(), dv[kv:kv + 1].cpu().numpy()
+        for q0, q1 in ((200, 232), (5000, 5032), (S - 32, S)):
+            got = O[b, h, q0:q1].float().cpu().numpy()
+            std = oracle.bf16_decode(oracle.attn_fwd_fp8(q, k, v, a, bb, c, scale, True, q_range=(q0, q1), rescale_threshold=0.0)[0])[0, 0, q0:q1]
+            lazy = oracle.bf16_decode(oracle.attn_fwd_fp8(q, k, v, a, bb, c, scale, True, q_range=(q0, q1))[0])[0, 0, q0:q1]
+            exact = _exact_fp8_attention_rows(oracle, q, k, v, a[0], bb[0], c[0], scale, q0, q1)
+            worst["std"] = max(worst["std"], rel_fro(got, std))
+            worst["lazy"] = max(worst["lazy"], rel_fro(got, lazy))
+            worst["gpu_exact"] = max(worst["gpu_exact"], rel_fro(got, exact))
+            worst["std_exact"] = max(worst["std_exact"], rel_fro(std, exact))
+    print("fp8 attention cfg4 sampled rows, worst rel. Frobenius error:", {k: round(v, 5) for k, v in worst.items()})
+    assert worst["lazy"] <= 1e-2
+    assert worst["gpu_exact"] <= 1.15 * worst["std_exact"] + 1e-3
+    assert worst["std"] <= 2.0 * worst["std_exact"] + 1e-3
+
+
 def test_causal_mask_tile_bits_match_oracle(pkg, oracle, dev):
     for q_base, k_base, tm, tn in ((0, 0, 128, 128), (128, 0, 128, 128), (0, 128, 128, 128), (256, 384, 128, 128),
                                    (64, 96, 16, 48), (5, 3, 7, 9), (4096 - 128, 4096 - 128, 128, 128)):

@@ -250,3 +250,20 @@ def test_fused_operator_goldens(oracle, golden):
         O, L = oracle.attn_fwd_bf16_qkv(g["Q"], g["K"], g["V"], float(g["scale"]), causal)
         assert np.abs(oracle.bf16_decode(O) - g["O_" + name]).max() < 1e-2
         assert np.abs(L - g["LSE_" + name]).max() < 1e-4
+
+
+def test_fp8_attention_oracle_modes_agree_with_the_float64_fixture(oracle, golden):
+    """The two P-rounding points of the E4M3 attention oracle (lazy reference maximum, as the sm100 kernel takes it; standard
+    per-tile running maximum) are two roundings of the same softmax: both sit at the E4M3 rounding noise of P from the float64
+    fixture (P unquantised there), and no further from each other than twice that."""
+    g = golden["attention_small"]
+    args = (g["Q8"], g["K8"], g["V8"], g["dq"], g["dk"], g["dv"], float(g["scale"]), True)
+    lazy = oracle.bf16_decode(oracle.attn_fwd_fp8(*args)[0])
+    std, lse_std = oracle.attn_fwd_fp8(*args, rescale_threshold=0.0)
+    std = oracle.bf16_decode(std)
+    want = g["O8_causal"]
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    e_lazy, e_std, e_between = rel(lazy, want), rel(std, want), rel(lazy, std)
+    assert e_lazy <= 4e-2 and e_std <= 4e-2
+    assert e_between <= 2.0 * max(e_lazy, e_std)
+    assert np.abs(lse_std - g["LSE8_causal"]).max() <= 1e-3

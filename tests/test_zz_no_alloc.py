@@ -7,7 +7,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_static_scratch_entry_matches_caller_scratch_entry_twice(pkg, dev):
+def test_static_scratch_entry_matches_caller_scratch_entry_twice(pkg, oracle, dev):
     B, Hq, Hkv, Sq, Skv, splits = 2, 8, 2, 4, 3000, 5
     Q, _, _, scale = pkg.synth.bf16_attention_inputs(B, Hq, Sq, 128, seed=31, Hkv=Hkv, device=dev)
     _, K, V, _ = pkg.synth.bf16_attention_inputs(B, Hkv, Skv, 128, seed=32, device=dev)
@@ -27,6 +27,13 @@ def test_static_scratch_entry_matches_caller_scratch_entry_twice(pkg, dev):
         assert torch.equal(L, want_L), f"call {call}: LSE differs from the caller-scratch entry point"
     free_after, _ = torch.cuda.mem_get_info(dev)
     assert free_after == free_before               # nothing was allocated on the device by the two calls
+    # and against the CPU oracle directly, so that this file stands on its own
+    import numpy as np
+
+    u16 = lambda t: t.cpu().view(torch.uint16).numpy()
+    Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, True)
+    assert np.abs(O.float().cpu().numpy() - oracle.bf16_decode(Ow)).max() <= 2e-2      # the bf16 attention bar
+    assert np.abs(L.cpu().numpy() - Lw).max() <= 1e-3
 
 
 def test_static_scratch_entry_rejects_what_does_not_fit(pkg, dev):
