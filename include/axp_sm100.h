@@ -258,6 +258,11 @@ int axp_sm100_selftest_bounded_wait(int64_t limit_cycles, void* stream, uint32_t
  *                               2 / 3 / 4 = 2 / 4 / 3 of every 8 pairs as a polynomial on the FMA pipe
  *   "attn.p_operand"            E4M3 attention: 1 = P reaches the P.V MMA in tensor memory,
  *                               2 = through shared memory (the next Q.K^T then overlaps the softmax)
+ *   "attn.rescale"              prefill attention: when a row's reference maximum advances.  1 = on every new maximum
+ *                               (the standard online softmax; P <= 1, the largest weight of a tile is exact in E4M3);
+ *                               2 = lazily, when a tile maximum exceeds it by more than 2^8 (the default: 13-15 % faster;
+ *                               for E4M3 P the rounding noise against exact attention is about 1.7 times the standard
+ *                               rule's on peaked softmax rows, for bf16 P there is no measurable difference)
  *   "attn.kv_tile"              bf16 attention: 64 or 128 keys per KV tile (64: two S buffers per Q tile in
  *                               tensor memory, the next Q.K^T never waits for the softmax)
  *   "attn.issuers"              1 or 2 threads issuing the attention MMAs (2: one per Q tile)

@@ -53,6 +53,7 @@ constexpr int kMaxKvStages = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
+constexpr float kDefaultRescaleFp8 = 8.0f;  // E4M3 prefill kernels (0 = standard online softmax)
 constexpr int kDefaultExpModeBf16 = 1;   // measured on cfg3 (64-key tiles, two issuers): 2/8 983, SFU only 970 TFLOP/s
 constexpr int kDefaultExpModeFp8 = 1;    // measured on cfg4: 2/8 1281, SFU only 1256, 3/8 1273, 4/8 1272 TFLOP/s
 constexpr bool kDefaultPSmemFp8 = true;
@@ -118,6 +119,7 @@ struct AttnParams {
 #endif
     // split-KV: CTA z of gridDim.z visits KV tiles [z * tiles_per_split, (z + 1) * tiles_per_split) and, when
     // splits > 1, leaves its unnormalised accumulator (fp32) and (m * c, l) per row in scratch memory
+    float rescale_thr;     // log2 units: the reference maximum of a row advances when a tile maximum exceeds it by more than this
     int splits;
     int partial;           // 1: leave partial results (always when splits > 1; also for one share of a KV-sharded call)
     int causal_off;        // under the causal mask query position i (inside its head) sees local keys <= i + causal_off;
@@ -690,7 +692,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (j == 0) {
                 m_used = (mx == -INFINITY) ? 0.0f : mx;
             } else {
-                const bool grow = (mx - m_used) * c > kRescaleThreshold;
+                const bool grow = (mx - m_used) * c > p.rescale_thr;
                 if (__any_sync(0xffffffffu, grow)) {
                     float factor = 1.0f;
                     if (grow) {
@@ -1522,6 +1524,11 @@ int launch_attn(const void* Q, const void* K, const void* V, const float* dq, co
 #endif
     // tuning option "attn.issuers": 0 = library default, 1 or 2 MMA-issuing threads
     const int iss_opt = option_slot(kOptAttnIssuers).load(std::memory_order_relaxed);
+    {
+        // option "attn.rescale": 0 library default, 1 = standard online softmax (advance on every new maximum), 2 = lazy (2^8)
+        const int r = option_slot(kOptAttnRescale).load(std::memory_order_relaxed);
+        p.rescale_thr = r == 1 ? 0.0f : r == 2 ? kRescaleThreshold : (kFp8 ? kDefaultRescaleFp8 : kRescaleThreshold);
+    }
     p.two_issuers = (iss_opt == 1 || iss_opt == 2) ? int(iss_opt == 2) : 1;   // measured with two: bf16 +12 %, E4M3 +4 %
 
     const int64_t heads = bh_end - bh_begin;

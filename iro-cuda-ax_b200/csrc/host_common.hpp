@@ -88,7 +88,7 @@ inline int check_register_pool(Kernel kernel, int threads, int needed_regs_total
 }
 
 // Process-wide tuning options set through axp_sm100_set_option (0 = library default).
-enum OptionId { kOptGemmEpiWg = 0, kOptGemmCtaGroup = 1, kOptAttnPolyExp = 2, kOptGemmExperiment = 3, kOptAttnPOperand = 4, kOptAttnKvTile = 5, kOptAttnIssuers = 6, kOptGemmFp8Tile = 7, kOptAttnDecode = 8, kOptCount = 9 };
+enum OptionId { kOptGemmEpiWg = 0, kOptGemmCtaGroup = 1, kOptAttnPolyExp = 2, kOptGemmExperiment = 3, kOptAttnPOperand = 4, kOptAttnKvTile = 5, kOptAttnIssuers = 6, kOptGemmFp8Tile = 7, kOptAttnDecode = 8, kOptAttnRescale = 9, kOptCount = 10 };
 std::atomic<int>& option_slot(int id);   // defined in shim.cu
 std::atomic<long long>& debug_pointer();  // defined in shim.cu; device buffer for latency experiments
 

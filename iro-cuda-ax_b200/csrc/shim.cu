@@ -130,6 +130,11 @@ extern "C" int axp_sm100_set_option(const char* name, int64_t value) {
         axp_shim::option_slot(axp_shim::kOptAttnDecode).store(int(value));
         return AXP_OK;
     }
+    if (!strcmp(name, "attn.rescale")) {   // prefill attention: 0 default, 1 = reference maximum advanced on every new maximum, 2 = lazily (2^8)
+        if (value < 0 || value > 2) return axp_shim::fail(AXP_ERR_BAD_ARG, "attn.rescale must be 0, 1 or 2");
+        axp_shim::option_slot(axp_shim::kOptAttnRescale).store(int(value));
+        return AXP_OK;
+    }
     if (!strcmp(name, "attn.kv_tile")) {   // bf16 attention: keys per KV tile, 0 default, 64 or 128
         if (value != 0 && value != 64 && value != 128) return axp_shim::fail(AXP_ERR_BAD_ARG, "attn.kv_tile must be 0, 64 or 128");
         axp_shim::option_slot(axp_shim::kOptAttnKvTile).store(int(value));

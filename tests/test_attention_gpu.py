@@ -155,18 +155,29 @@ def _exact_fp8_attention_rows(oracle, q, k, v, dq, dk, dv, scale, q0, q1):
 
 def test_fp8_attention_against_the_standard_online_softmax(pkg, oracle, dev):
     """The E4M3 recipe rounds P to E4M3 before P.V, so WHERE P is taken (against which reference maximum) decides which
-    values are rounded.  The kernel advances its reference lazily; the parity oracle used elsewhere follows that rule.
-    This test holds the kernel against an oracle that does not know the kernel: the standard online softmax (per-tile
-    running maximum, P <= 1), and against exact float64 attention with unquantised P, on cfg4's shape (sampled heads
-    and rows) and on a small full problem.
-      (i)   GPU vs standard-recipe oracle: two roundings of different P values, i.e. twice the recipe's own rounding noise;
-      (ii)  GPU vs lazy-rule oracle: same rounding points, the <= 1e-2 bar;
-      (iii) GPU vs exact: must be no further from the truth than the standard recipe is (within 15 %)."""
+    values are rounded.  By default the kernel advances its reference lazily (a new maximum must exceed it by 2^8), and
+    the parity oracle used elsewhere follows that rule.  This test holds the kernel against an oracle that does not know
+    the kernel - the standard online softmax (per-tile running maximum, P <= 1) - and against exact float64 attention
+    with unquantised P, on cfg4's shape (sampled heads and rows):
+      * option attn.rescale = 1 makes the kernel take the standard rule: it must then match the standard oracle within
+        the 1e-2 bar (same rounding points, nothing shared with the kernel's schedule);
+      * default (lazy): matches the lazy-rule oracle within 1e-2; against the TRUTH both recipes show the E4M3 rounding
+        noise of P, a few percent on these peaked softmax rows.  Under the standard rule the largest weight of a tile is
+        exactly 1 and therefore exact in E4M3; under the lazy rule it is an arbitrary value in [1, 2^8] and is rounded, so
+        the lazy recipe is the noisier one (measured pooled error 0.021 against 0.0125): bounded here at twice the
+        standard recipe's."""
     B, Hq, Hkv, S, D = 4, 64, 8, 8192, 128
     Q, K, V, dq, dk, dv, scale = pkg.synth.fp8_attention_inputs(B, Hq, Hkv, S, D, seed=0, device=dev)
-    O, _ = pkg.ops.attn_fwd_fp8(Q, K, V, dq, dk, dv, scale, True)
-    pkg.ops.check_status(dev)
-    worst = {"std": 0.0, "lazy": 0.0, "gpu_exact": 0.0, "std_exact": 0.0}
+    outs = {}
+    try:
+        for mode, opt in (("lazy", 0), ("standard", 1)):
+            pkg.capi.set_option("attn.rescale", opt)
+            outs[mode], _ = pkg.ops.attn_fwd_fp8(Q, K, V, dq, dk, dv, scale, True)
+            pkg.ops.check_status(dev)
+    finally:
+        pkg.capi.set_option("attn.rescale", 0)
+    worst = {"lazy_kernel_vs_lazy_oracle": 0.0, "std_kernel_vs_std_oracle": 0.0, "lazy_kernel_vs_std_oracle": 0.0}
+    sq = {"lazy_kernel": 0.0, "std_kernel": 0.0, "std_oracle": 0.0, "exact": 0.0}      # squared error against exact attention, pooled
     for bh in (3, 130, B * Hq - 2):
         b, h = divmod(bh, Hq)
         hk = h // (Hq // Hkv)
@@ -174,18 +185,25 @@ def test_fp8_attention_against_the_standard_online_softmax(pkg, oracle, dev):
         q, k, v = u8(Q[b:b + 1, h:h + 1]), u8(K[b:b + 1, hk:hk + 1]), u8(V[b:b + 1, hk:hk + 1])
         a, bb, c = dq[bh:bh + 1].cpu().numpy(), dk[kv:kv + 1].cpu().numpy(), dv[kv:kv + 1].cpu().numpy()
         for q0, q1 in ((200, 232), (5000, 5032), (S - 32, S)):
-            got = O[b, h, q0:q1].float().cpu().numpy()
+            got_lazy = outs["lazy"][b, h, q0:q1].float().cpu().numpy()
+            got_std = outs["standard"][b, h, q0:q1].float().cpu().numpy()
             std = oracle.bf16_decode(oracle.attn_fwd_fp8(q, k, v, a, bb, c, scale, True, q_range=(q0, q1), rescale_threshold=0.0)[0])[0, 0, q0:q1]
             lazy = oracle.bf16_decode(oracle.attn_fwd_fp8(q, k, v, a, bb, c, scale, True, q_range=(q0, q1))[0])[0, 0, q0:q1]
             exact = _exact_fp8_attention_rows(oracle, q, k, v, a[0], bb[0], c[0], scale, q0, q1)
-            worst["std"] = max(worst["std"], rel_fro(got, std))
-            worst["lazy"] = max(worst["lazy"], rel_fro(got, lazy))
-            worst["gpu_exact"] = max(worst["gpu_exact"], rel_fro(got, exact))
-            worst["std_exact"] = max(worst["std_exact"], rel_fro(std, exact))
-    print("fp8 attention cfg4 sampled rows, worst rel. Frobenius error:", {k: round(v, 5) for k, v in worst.items()})
-    assert worst["lazy"] <= 1e-2
-    assert worst["gpu_exact"] <= 1.15 * worst["std_exact"] + 1e-3
-    assert worst["std"] <= 2.0 * worst["std_exact"] + 1e-3
+            worst["lazy_kernel_vs_lazy_oracle"] = max(worst["lazy_kernel_vs_lazy_oracle"], rel_fro(got_lazy, lazy))
+            worst["std_kernel_vs_std_oracle"] = max(worst["std_kernel_vs_std_oracle"], rel_fro(got_std, std))
+            worst["lazy_kernel_vs_std_oracle"] = max(worst["lazy_kernel_vs_std_oracle"], rel_fro(got_lazy, std))
+            sq["lazy_kernel"] += float(((got_lazy - exact) ** 2).sum())
+            sq["std_kernel"] += float(((got_std - exact) ** 2).sum())
+            sq["std_oracle"] += float(((std - exact) ** 2).sum())
+            sq["exact"] += float((exact ** 2).sum())
+    pooled = {k: (sq[k] / sq["exact"]) ** 0.5 for k in ("lazy_kernel", "std_kernel", "std_oracle")}
+    print("fp8 attention cfg4 sampled rows: worst rel. Frobenius error", {k: round(v, 5) for k, v in worst.items()},
+          "; pooled error against exact attention", {k: round(v, 5) for k, v in pooled.items()})
+    assert worst["std_kernel_vs_std_oracle"] <= 1e-2          # the independent check
+    assert worst["lazy_kernel_vs_lazy_oracle"] <= 1e-2
+    assert pooled["std_kernel"] <= 1.1 * pooled["std_oracle"] + 1e-3
+    assert pooled["lazy_kernel"] <= 2.0 * pooled["std_oracle"] + 1e-3
 
 
 def test_causal_mask_tile_bits_match_oracle(pkg, oracle, dev):
