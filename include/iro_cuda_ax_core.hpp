@@ -52,6 +52,16 @@ struct concat<type_list<As...>, type_list<Bs...>> {
 template <class A, class B>
 using concat_t = typename concat<A, B>::type;
 
+// first element of a non-empty list
+template <class List>
+struct front;
+template <class T, class... Ts>
+struct front<type_list<T, Ts...>> {
+    using type = T;
+};
+template <class List>
+using front_t = typename front<List>::type;
+
 template <class T, class List>
 struct contains;
 template <class T, class... Ts>

@@ -1609,6 +1609,7 @@ int launch_attn(const void* Q, const void* K, const void* V, const float* dq, co
 extern "C" int axp_sm100_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, float* LSE, int64_t B,
                                        int64_t Hq, int64_t Hkv, int64_t S, int64_t D, float scale, int causal,
                                        int64_t bh_begin, int64_t bh_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_attn_fwd_bf16");
     return launch_attn<false>(Q, K, V, nullptr, nullptr, nullptr, O, LSE, B, Hq, Hkv, S, S, D, scale, causal, 1, nullptr, 0,
                               bh_begin, bh_end, stream, status_dev);
 }
@@ -1622,6 +1623,7 @@ extern "C" int axp_sm100_attn_fwd_bf16_splitkv(const void* Q, const void* K, con
                                                int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Skv, int64_t D, float scale,
                                                int causal, int64_t num_splits, void* scratch, int64_t scratch_bytes,
                                                int64_t bh_begin, int64_t bh_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_attn_fwd_bf16_splitkv");
     return launch_attn<false>(Q, K, V, nullptr, nullptr, nullptr, O, LSE, B, Hq, Hkv, Sq, Skv, D, scale, causal, num_splits,
                               scratch, scratch_bytes, bh_begin, bh_end, stream, status_dev, /*stack_gqa=*/true);
 }
@@ -1635,6 +1637,7 @@ extern "C" int axp_sm100_attn_fwd_bf16_kvshard(const void* Q, const void* K, con
                                                int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Skv_local, int64_t kv_pos0,
                                                int64_t Skv_total, int64_t D, float scale, int causal, int64_t bh_begin,
                                                int64_t bh_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_attn_fwd_bf16_kvshard");
     if (!partial) return axp_shim::fail(AXP_ERR_BAD_ARG, "attn kvshard: partial buffer is null");
     // O and LSE are not written by a KV-shard pass: the partial buffer stands in for the (non-null) output argument
     return launch_attn<false>(Q, K, V, nullptr, nullptr, nullptr, partial, nullptr, B, Hq, Hkv, Sq, Skv_local, D, scale, causal, 1, partial,
@@ -1643,6 +1646,7 @@ extern "C" int axp_sm100_attn_fwd_bf16_kvshard(const void* Q, const void* K, con
 
 extern "C" int axp_sm100_attn_combine_partials(const void* partials, int64_t num_shares, int64_t share_stride_bytes, void* O, float* LSE,
                                                int64_t rows, void* stream) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_attn_combine_partials");
     using namespace axp_shim;
     if (!partials || !O) return fail(AXP_ERR_BAD_ARG, "attn combine: null pointer argument");
     if (num_shares < 1 || num_shares > 4096 || rows <= 0) return fail(AXP_ERR_BAD_ARG, "attn combine: bad share or row count");
@@ -1670,6 +1674,7 @@ extern "C" int axp_sm100_attn_fwd_bf16_splitkv_static(const void* Q, const void*
                                                       int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Skv, int64_t D,
                                                       float scale, int causal, int64_t num_splits, int64_t bh_begin,
                                                       int64_t bh_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_attn_fwd_bf16_splitkv_static");
     using namespace axp_shim;
     if (num_splits < 1 || Sq <= 0 || bh_begin < 0 || bh_end < bh_begin)
         return fail(AXP_ERR_BAD_ARG, "attn split-KV (static scratch): bad split count, query length or head range");
@@ -1698,6 +1703,7 @@ extern "C" int axp_sm100_attn_fwd_fp8_splitkv(const void* Q, const void* K, cons
                                               int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Skv, int64_t D, float scale, int causal,
                                               int64_t num_splits, void* scratch, int64_t scratch_bytes, int64_t bh_begin,
                                               int64_t bh_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_attn_fwd_fp8_splitkv");
     return launch_attn<true>(Q, K, V, q_descale, k_descale, v_descale, O, LSE, B, Hq, Hkv, Sq, Skv, D, scale, causal, num_splits,
                              scratch, scratch_bytes, bh_begin, bh_end, stream, status_dev, /*stack_gqa=*/true);
 }
@@ -1706,6 +1712,7 @@ extern "C" int axp_sm100_attn_fwd_fp8(const void* Q, const void* K, const void* 
                                       const float* k_descale, const float* v_descale, void* O, float* LSE, int64_t B,
                                       int64_t Hq, int64_t Hkv, int64_t S, int64_t D, float scale, int causal,
                                       int64_t bh_begin, int64_t bh_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_attn_fwd_fp8");
     return launch_attn<true>(Q, K, V, q_descale, k_descale, v_descale, O, LSE, B, Hq, Hkv, S, S, D, scale, causal, 1, nullptr, 0,
                              bh_begin, bh_end, stream, status_dev);
 }

@@ -1037,24 +1037,28 @@ extern "C" int axp_sm100_gemm_fp8_blockscaled_swiglu(const void* X, const void* 
                                                      const float* sWu, void* H, int64_t M, int64_t N, int64_t K, int64_t ldx,
                                                      int64_t ldwg, int64_t ldwu, int64_t ldh, int64_t n_begin, int64_t n_end,
                                                      void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_fp8_blockscaled_swiglu");
     return launch_gated_fp8(X, Wg, Wu, sX, sWg, sWu, H, M, N, K, ldx, ldwg, ldwu, ldh, n_begin, n_end, stream, status_dev);
 }
 
 extern "C" int axp_sm100_gemm_bf16_swiglu(const void* X, const void* Wg, const void* Wu, void* H, int64_t M, int64_t N,
                                           int64_t K, int64_t ldx, int64_t ldwg, int64_t ldwu, int64_t ldh,
                                           int64_t n_begin, int64_t n_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_bf16_swiglu");
     return launch_gated(X, Wg, Wu, H, M, N, K, ldx, ldwg, ldwu, ldh, n_begin, n_end, stream, status_dev);
 }
 
 extern "C" int axp_sm100_gemm_fp8_blockscaled(const void* A, const void* B, const float* sA, const float* sB, void* C,
                                               int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                                               int64_t n_begin, int64_t n_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_fp8_blockscaled");
     return launch_gemm<true>(A, B, sA, sB, nullptr, AXP_ACT_NONE, C, M, N, K, lda, ldb, ldc, n_begin, n_end, stream, status_dev);
 }
 
 extern "C" int axp_sm100_gemm_bf16_lincomb(const void* A, const void* B, const void* Cin, void* D, float alpha, float beta, int64_t M,
                                            int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldcin, int64_t ldd,
                                            int64_t n_begin, int64_t n_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_bf16_lincomb");
     if (!Cin) return axp_shim::fail(AXP_ERR_BAD_ARG, "gemm lincomb: C input is null");
     return launch_gemm<false>(A, B, nullptr, nullptr, nullptr, AXP_ACT_NONE, D, M, N, K, lda, ldb, ldd, n_begin, n_end, stream, status_dev,
                               Cin, ldcin, alpha, beta);
@@ -1064,6 +1068,7 @@ extern "C" int axp_sm100_gemm_fp8_blockscaled_lincomb(const void* A, const void*
                                                       void* D, float alpha, float beta, int64_t M, int64_t N, int64_t K, int64_t lda,
                                                       int64_t ldb, int64_t ldcin, int64_t ldd, int64_t n_begin, int64_t n_end,
                                                       void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_fp8_blockscaled_lincomb");
     if (!Cin) return axp_shim::fail(AXP_ERR_BAD_ARG, "gemm lincomb: C input is null");
     return launch_gemm<true>(A, B, sA, sB, nullptr, AXP_ACT_NONE, D, M, N, K, lda, ldb, ldd, n_begin, n_end, stream, status_dev, Cin,
                              ldcin, alpha, beta);
@@ -1073,6 +1078,7 @@ extern "C" int axp_sm100_gemm_fp8_blockscaled_bias_act(const void* A, const void
                                                        const float* bias, void* C, int64_t M, int64_t N, int64_t K,
                                                        int64_t lda, int64_t ldb, int64_t ldc, int64_t n_begin,
                                                        int64_t n_end, int act, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_fp8_blockscaled_bias_act");
     if (!bias) return axp_shim::fail(AXP_ERR_BAD_ARG, "gemm bias_act: bias is null");
     return launch_gemm<true>(A, B, sA, sB, bias, act, C, M, N, K, lda, ldb, ldc, n_begin, n_end, stream, status_dev);
 }
@@ -1080,6 +1086,7 @@ extern "C" int axp_sm100_gemm_fp8_blockscaled_bias_act(const void* A, const void
 extern "C" int axp_sm100_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                                    int64_t lda, int64_t ldb, int64_t ldc, int64_t n_begin, int64_t n_end,
                                    void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_bf16");
     return launch_gemm<false>(A, B, nullptr, nullptr, nullptr, AXP_ACT_NONE, C, M, N, K, lda, ldb, ldc, n_begin, n_end, stream,
                               status_dev);
 }
@@ -1087,6 +1094,7 @@ extern "C" int axp_sm100_gemm_bf16(const void* A, const void* B, void* C, int64_
 extern "C" int axp_sm100_gemm_bf16_bias_act(const void* A, const void* B, const float* bias, void* C, int64_t M, int64_t N,
                                             int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t n_begin,
                                             int64_t n_end, int act, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_bf16_bias_act");
     if (!bias) return axp_shim::fail(AXP_ERR_BAD_ARG, "gemm bias_act: bias is null");
     return launch_gemm<false>(A, B, nullptr, nullptr, bias, act, C, M, N, K, lda, ldb, ldc, n_begin, n_end, stream, status_dev);
 }

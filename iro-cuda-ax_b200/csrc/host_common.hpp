@@ -11,6 +11,8 @@
 #include <cstdint>
 #include <cstdio>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "axp/realize/sm100_host.hpp"
 #include "axp_sm100.h"
 
@@ -91,6 +93,15 @@ inline int check_register_pool(Kernel kernel, int threads, int needed_regs_total
 enum OptionId { kOptGemmEpiWg = 0, kOptGemmCtaGroup = 1, kOptAttnPolyExp = 2, kOptGemmExperiment = 3, kOptAttnPOperand = 4, kOptAttnKvTile = 5, kOptAttnIssuers = 6, kOptGemmFp8Tile = 7, kOptAttnDecode = 8, kOptAttnRescale = 9, kOptCount = 10 };
 std::atomic<int>& option_slot(int id);   // defined in shim.cu
 std::atomic<long long>& debug_pointer();  // defined in shim.cu; device buffer for latency experiments
+
+// NVTX range around the host side of an entry point (argument checks, tensor-map encoding, launch), so that a timeline
+// tool shows which C-ABI call a kernel belongs to.  NVTX is header-only and costs a few nanoseconds when no tool is attached.
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

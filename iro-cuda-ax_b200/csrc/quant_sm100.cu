@@ -164,6 +164,7 @@ rmsnorm_quantize_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, const __n
 
 extern "C" int axp_sm100_rmsnorm_quantize_rows_e4m3(const void* X, const void* W, float eps, void* Q, float* scales, int64_t M,
                                                     int64_t K, int64_t ldx, int64_t ldq, void* stream) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_rmsnorm_quantize_rows_e4m3");
     using namespace axp_shim;
     if (!X || !W || !Q || !scales) return fail(AXP_ERR_BAD_ARG, "rmsnorm quantize: null pointer argument");
     if (M <= 0 || K <= 0) return fail(AXP_ERR_BAD_ARG, "rmsnorm quantize: M and K must be positive");
@@ -192,6 +193,7 @@ extern "C" int axp_sm100_rmsnorm_quantize_rows_e4m3(const void* X, const void* W
 
 extern "C" int axp_sm100_quantize_rows_e4m3(const void* X, void* Q, float* scales, int64_t M, int64_t K, int64_t ldx,
                                             int64_t ldq, void* stream) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_quantize_rows_e4m3");
     using namespace axp_shim;
     if (!X || !Q || !scales) return fail(AXP_ERR_BAD_ARG, "quantize: null pointer argument");
     if (M <= 0 || K <= 0) return fail(AXP_ERR_BAD_ARG, "quantize: M and K must be positive");

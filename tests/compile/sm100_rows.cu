@@ -153,6 +153,9 @@ static_assert(axp::kit::sm100::detail::has_execute<axp::realize::sm100::ScalePro
               axp::kit::sm100::detail::has_execute<axp::realize::sm100::TmemLoadWait>::value &&
               axp::kit::sm100::detail::has_execute<axp::realize::sm100::HostTensorMapEncoder>::value &&
               axp::kit::sm100::detail::has_execute<axp::realize::sm100::CausalMaskPred>::value);
+// calling a realization the way the reference's example does (examples/sm89_ax_div_example.cu:20-41): bind, take the leaf, execute
+using PromoteBound = axp::kit::sm100::bind<px::ScalePromoteAccumulator<axp::recipe::E4M3BlockScaledAccF32OutBF16>>;
+static_assert(std::is_same_v<iro::util::front_t<PromoteBound::realization::leaves>, axp::realize::sm100::ScalePromoteFma>);
 struct NoExecuteProbe {};
 static_assert(!axp::kit::sm100::detail::has_execute<NoExecuteProbe>::value);
 static_assert(iro::util::contains<axp::realize::sm100::Tcgen05Mma<1, false>, axp::kit::sm100::bind<MmaFp8>::realization::leaves>::value);
@@ -179,5 +182,9 @@ __global__ void axp_sm100_leaf_instantiation(unsigned* out) {
         out[1] = rz::PackBf16x2::execute(1.0f, 2.0f);
         out[2] = rz::PackE4m3x4::execute(1.0f, 2.0f, 500.0f, -500.0f);
         out[3] = rz::causal_tile_skip(0, 128, 128) ? 1u : 0u;
+        float acc[2] = {1.0f, 2.0f};
+        const uint32_t partial[2] = {0x3f800000u, 0x40000000u};
+        iro::util::front_t<PromoteBound::realization::leaves>::execute(acc, partial, 0.5f);      // acc = {1.5, 3}
+        out[4] = __float_as_uint(acc[0] + acc[1]);
     }
 }
