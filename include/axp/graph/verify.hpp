@@ -1,11 +1,13 @@
 // Structural verification of a selected graph (reference include/axp/graph/verify.hpp:36-84):
 // every obligation has an id, the list has no duplicate, resources fit the capability
 // (checked when the composition is formed) and every obligation binds to an sm100
-// realization.
+// realization; and the contract flow of the list is closed (flow.hpp): every token an input port requires was provided
+// by an earlier obligation, by the graph's externals or by a loop-carried token that the list provides again.
 #pragma once
 #include <iro_cuda_ax_core.hpp>
 
 #include "../kits/sm100/index.hpp"
+#include "flow.hpp"
 
 namespace axp::graph {
 
@@ -31,7 +33,7 @@ constexpr bool verify_structure() {
 template <class G>
 constexpr bool verify_contract_flow() {
     return axp::kit::sm100::binds_all<typename G::obligations>::value && G::smem_bytes <= G::cap::max_smem_bytes &&
-           G::tmem_cols <= G::cap::tmem_columns;
+           G::tmem_cols <= G::cap::tmem_columns && flow_closed<G>();
 }
 
 template <class G>

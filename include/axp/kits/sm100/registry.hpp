@@ -64,41 +64,41 @@ struct all_have_execute<type_list<Ls...>> : std::bool_constant<(sizeof...(Ls) > 
 #if defined(__CUDACC__)
 AXP_SM100_REGISTER(AXP_T(class S, class E, int R), AXP_O(px::HostMakeTensorMap<S, E, R>), "tma.host_make_tensor_map",
                    rz::HostTensorMapEncoder);
-AXP_SM100_REGISTER(AXP_T(class S, int B, int N), AXP_O(px::StageRing<S, B, N, 2>), "stage.ring_2d", rz::BarrierInit,
+AXP_SM100_REGISTER(AXP_T(class S, int B, int N, int G), AXP_O(px::StageRing<S, B, N, 2, G>), "stage.ring_2d", rz::BarrierInit,
                    rz::BarrierExpectTx, rz::BulkTmaCopy2D, rz::BarrierWait, rz::MakeSmemDescKMajorSw128);
-AXP_SM100_REGISTER(AXP_T(class S, int B, int N), AXP_O(px::StageRing<S, B, N, 3>), "stage.ring_3d", rz::BarrierInit,
+AXP_SM100_REGISTER(AXP_T(class S, int B, int N, int G), AXP_O(px::StageRing<S, B, N, 3, G>), "stage.ring_3d", rz::BarrierInit,
                    rz::BarrierExpectTx, rz::BulkTmaCopy3D, rz::BarrierWait, rz::MakeSmemDescKMajorSw128,
                    rz::MakeSmemDescMnMajorSw128);
 AXP_SM100_REGISTER(template <>, px::BoundedBarrierWait, "sync.bounded_wait", rz::BarrierTryWait, rz::BarrierWait);
 AXP_SM100_REGISTER(AXP_T(int C, int G), AXP_O(px::TmemAllocate<C, G>), "tmem.alloc", rz::TmemAlloc<G>);
 AXP_SM100_REGISTER(AXP_T(int C, int G), AXP_O(px::TmemRelease<C, G>), "tmem.dealloc", rz::TmemDealloc<G>);
-AXP_SM100_REGISTER(AXP_T(int M, int N, int K, class EA, class EB, int G, px::Major BM),
-                   AXP_O(px::Tcgen05Mma<M, N, K, EA, EB, G, px::OperandSource::shared, BM>), "compute.tcgen05_mma_ss",
+AXP_SM100_REGISTER(AXP_T(int M, int N, int K, class EA, class EB, int G, px::Major BM, class SA, class SB, class SD),
+                   AXP_O(px::Tcgen05Mma<M, N, K, EA, EB, G, px::OperandSource::shared, BM, SA, SB, SD>), "compute.tcgen05_mma_ss",
                    rz::Tcgen05Mma<G, (EA::bytes == 2)>, rz::Tcgen05FenceAfter);
-AXP_SM100_REGISTER(AXP_T(int M, int N, int K, class EA, class EB, px::Major BM),
-                   AXP_O(px::Tcgen05Mma<M, N, K, EA, EB, 1, px::OperandSource::tmem, BM>), "compute.tcgen05_mma_ts",
+AXP_SM100_REGISTER(AXP_T(int M, int N, int K, class EA, class EB, px::Major BM, class SA, class SB, class SD),
+                   AXP_O(px::Tcgen05Mma<M, N, K, EA, EB, 1, px::OperandSource::tmem, BM, SA, SB, SD>), "compute.tcgen05_mma_ts",
                    rz::Tcgen05MmaTmemA<(EA::bytes == 2)>, rz::Tcgen05FenceAfter);
-AXP_SM100_REGISTER(AXP_T(int G), AXP_O(px::Tcgen05Commit<G>), "compute.tcgen05_commit", rz::Tcgen05Commit<G>);
-AXP_SM100_REGISTER(AXP_T(int C), AXP_O(px::TmemToRegisters<C>), "tmem.ld_32x32b", rz::TmemLoad32x32, rz::TmemLoadWait,
+AXP_SM100_REGISTER(AXP_T(int G, class S), AXP_O(px::Tcgen05Commit<G, S>), "compute.tcgen05_commit", rz::Tcgen05Commit<G>);
+AXP_SM100_REGISTER(AXP_T(int C, class S), AXP_O(px::TmemToRegisters<C, S>), "tmem.ld_32x32b", rz::TmemLoad32x32, rz::TmemLoadWait,
                    rz::Tcgen05FenceBefore);
-AXP_SM100_REGISTER(AXP_T(int C), AXP_O(px::RegistersToTmem<C>), "tmem.st_32x32b", rz::TmemStore32x32, rz::TmemStoreWait,
+AXP_SM100_REGISTER(AXP_T(int C, class S), AXP_O(px::RegistersToTmem<C, S>), "tmem.st_32x32b", rz::TmemStore32x32, rz::TmemStoreWait,
                    rz::Tcgen05FenceBefore);
-AXP_SM100_REGISTER(AXP_T(int B, int N), AXP_O(px::RegistersToSharedOperand<B, N>), "stage.registers_to_shared_operand", rz::AsyncProxyFence,
+AXP_SM100_REGISTER(AXP_T(int B, int N, class S), AXP_O(px::RegistersToSharedOperand<B, N, S>), "stage.registers_to_shared_operand", rz::AsyncProxyFence,
                    rz::BarrierArrive, rz::MakeSmemDescKMajorSw128);
-AXP_SM100_REGISTER(AXP_T(class R), AXP_O(px::ScalePromoteAccumulator<R>), "scale.promote_fma", rz::ScalePromoteFma);
-AXP_SM100_REGISTER(AXP_T(class P), AXP_O(px::CastPack<iro::elem::f32, iro::elem::bf16, P>), "convert.pack_bf16x2",
+AXP_SM100_REGISTER(AXP_T(class R, class S, class SA, class SB), AXP_O(px::ScalePromoteAccumulator<R, S, SA, SB>), "scale.promote_fma", rz::ScalePromoteFma);
+AXP_SM100_REGISTER(AXP_T(class P, class SI, class SO), AXP_O(px::CastPack<iro::elem::f32, iro::elem::bf16, P, SI, SO>), "convert.pack_bf16x2",
                    rz::PackBf16x2);
-AXP_SM100_REGISTER(AXP_T(class P), AXP_O(px::CastPack<iro::elem::f32, iro::elem::e4m3, P>), "convert.pack_e4m3x4_sat",
+AXP_SM100_REGISTER(AXP_T(class P, class SI, class SO), AXP_O(px::CastPack<iro::elem::f32, iro::elem::e4m3, P, SI, SO>), "convert.pack_e4m3x4_sat",
                    rz::PackE4m3x4);
-AXP_SM100_REGISTER(AXP_T(class P), AXP_O(px::CastWeights<iro::elem::bf16, P>), "convert.weights_bf16x2", rz::PackBf16x2);
-AXP_SM100_REGISTER(AXP_T(class P), AXP_O(px::CastWeights<iro::elem::e4m3, P>), "convert.weights_e4m3x4_sat", rz::PackE4m3x4);
-AXP_SM100_REGISTER(AXP_T(class B, class A), AXP_O(px::BiasActivation<B, A>), "epilogue.bias_activation", rz::BiasActFma);
-AXP_SM100_REGISTER(AXP_T(class U, class A), AXP_O(px::GatedActivation<U, A>), "epilogue.gated_activation", rz::BiasActFma);
-AXP_SM100_REGISTER(AXP_T(class C, class A, class B), AXP_O(px::LinearCombination<C, A, B>), "epilogue.linear_combination", rz::BiasActFma);
-AXP_SM100_REGISTER(AXP_T(class E), AXP_O(px::StoreRowGlobal<E>), "store.row_vec16", rz::RowStoreVec16);
-AXP_SM100_REGISTER(AXP_T(int M, int N), AXP_O(px::CausalMaskPredicate<M, N>), "mask.causal_pred", rz::CausalMaskPred);
-AXP_SM100_REGISTER(template <>, px::RowSoftmaxStateUpdate, "softmax.row_state_exp2", rz::RowSoftmaxExp2);
-AXP_SM100_REGISTER(template <>, px::RescaleAccumulatorInTmem, "softmax.rescale_tmem", rz::TmemLoad32x32, rz::TmemStore32x32,
+AXP_SM100_REGISTER(AXP_T(class P, class S), AXP_O(px::CastWeights<iro::elem::bf16, P, S>), "convert.weights_bf16x2", rz::PackBf16x2);
+AXP_SM100_REGISTER(AXP_T(class P, class S), AXP_O(px::CastWeights<iro::elem::e4m3, P, S>), "convert.weights_e4m3x4_sat", rz::PackE4m3x4);
+AXP_SM100_REGISTER(AXP_T(class B, class A, class S), AXP_O(px::BiasActivation<B, A, S>), "epilogue.bias_activation", rz::BiasActFma);
+AXP_SM100_REGISTER(AXP_T(class U, class A, class S), AXP_O(px::GatedActivation<U, A, S>), "epilogue.gated_activation", rz::BiasActFma);
+AXP_SM100_REGISTER(AXP_T(class C, class A, class B, class S), AXP_O(px::LinearCombination<C, A, B, S>), "epilogue.linear_combination", rz::BiasActFma);
+AXP_SM100_REGISTER(AXP_T(class E, class S), AXP_O(px::StoreRowGlobal<E, S>), "store.row_vec16", rz::RowStoreVec16);
+AXP_SM100_REGISTER(AXP_T(int M, int N, class S), AXP_O(px::CausalMaskPredicate<M, N, S>), "mask.causal_pred", rz::CausalMaskPred);
+AXP_SM100_REGISTER(AXP_T(class S, class P, class St), AXP_O(px::RowSoftmaxStateUpdateOn<S, P, St>), "softmax.row_state_exp2", rz::RowSoftmaxExp2);
+AXP_SM100_REGISTER(AXP_T(class O_, class St), AXP_O(px::RescaleAccumulatorInTmemOn<O_, St>), "softmax.rescale_tmem", rz::TmemLoad32x32, rz::TmemStore32x32,
                    rz::TmemStoreWait);
 AXP_SM100_REGISTER(AXP_T(int P, int M), AXP_O(px::RoleRegisterBudget<P, M>), "specialize.setmaxnreg", rz::RegDealloc<P>,
                    rz::RegAlloc<M>);

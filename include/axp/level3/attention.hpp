@@ -9,6 +9,7 @@
 // and the accumulator rescale applied in place only when a row maximum grew.  The reference restricts attention inputs to f16/bf16
 // (include/axp/level3/attention.hpp:95-96); the E4M3 branch is an sm100 addition.
 #pragma once
+#include "../graph/flow.hpp"
 #include "../kits/intent.hpp"
 #include "../kits/sm100/index.hpp"
 #include "../protocol/sm100_contracts.hpp"
@@ -66,22 +67,41 @@ struct AttentionTileTcgen05Impl {
     static constexpr int kIssuers = 2;
     static constexpr bool causal = std::is_same_v<TileSkip, axp::intent::tile_skip::Causal>;
 
-    using qk = px::Tcgen05Mma<TileQ, kKvStep, kMmaK, in, in, 1, px::OperandSource::shared, px::Major::k>;
+    // wires: S = scores (tensor memory -> registers), P = weights (registers -> tensor or shared memory), O = the output
+    // accumulator in tensor memory and, after the last step, the packed result in registers and global memory; the per-row
+    // (m, l) state lives in registers of the row's thread
+    using S = axp::subject::AttentionS;
+    using P = axp::subject::AttentionP;
+    using O = axp::subject::Output;
+    using State = axp::subject::SoftmaxState;
+    using qk = px::Tcgen05Mma<TileQ, kKvStep, kMmaK, in, in, 1, px::OperandSource::shared, px::Major::k, QSubj, KSubj, S>;
     using pv = px::Tcgen05Mma<TileQ, HeadDim, kMmaK, in, in, 1, (kPThroughSmem ? px::OperandSource::shared : px::OperandSource::tmem),
-                              px::Major::mn>;
-    using p_route = std::conditional_t<kPThroughSmem, px::RegistersToSharedOperand<kQTileBytes, 2 * kQTilesPerCta>, px::RegistersToTmem<32>>;
+                              px::Major::mn, P, VSubj, O>;
+    using p_route = std::conditional_t<kPThroughSmem, px::RegistersToSharedOperand<kQTileBytes, 2 * kQTilesPerCta, P>, px::RegistersToTmem<32, P>>;
+    // one step of the KV loop, then the epilogue of the Q tile
     using obligations = iro::util::type_list<
         px::HostMakeTensorMap<QSubj, in, 3>, px::HostMakeTensorMap<KSubj, in, 3>, px::HostMakeTensorMap<VSubj, in, 3>,
         px::StageRing<QSubj, kQTileBytes, kQTilesPerCta, 3>, px::StageRing<KSubj, kKvTileBytes, Stages, 3>,
         px::StageRing<VSubj, kKvTileBytes, Stages, 3>, px::RoleRegisterBudget<kProducerRegs, kSoftmaxRegs>, px::TmemAllocate<kTmemCols, 1>,
-        px::BoundedBarrierWait, qk, px::Tcgen05Commit<1>, px::TmemToRegisters<32>, px::CausalMaskPredicate<TileQ, kKvStep>,
-        px::RowSoftmaxStateUpdate, px::RescaleAccumulatorInTmem, px::CastWeights<in, typename Recipe::fp8_policy>,
-        p_route, pv, px::CastPack<iro::elem::f32, out, typename Recipe::fp8_policy>, px::StoreRowGlobal<out>,
+        px::BoundedBarrierWait, qk, px::Tcgen05Commit<1, S>, px::TmemToRegisters<32, S>, px::CausalMaskPredicate<TileQ, kKvStep, S>,
+        px::RowSoftmaxStateUpdateOn<S, P, State>, px::RescaleAccumulatorInTmemOn<O, State>, px::CastWeights<in, typename Recipe::fp8_policy, P>,
+        p_route, pv, px::Tcgen05Commit<1, O>, px::TmemToRegisters<32, O>,
+        px::CastPack<iro::elem::f32, out, typename Recipe::fp8_policy, O, O>, px::StoreRowGlobal<out, O>,
         px::TmemRelease<kTmemCols, 1>>;
+    using external_list = iro::util::concat_t<axp::graph::external_tokens<axp::subject::in_global<QSubj>>,
+                                              iro::util::concat_t<axp::graph::external_tokens<axp::subject::in_global<KSubj>>,
+                                                                  axp::graph::external_tokens<axp::subject::in_global<VSubj>>>>;
+    // carried from the previous step of the KV loop: the accumulator that the last P.V commit published (the rescale
+    // reads it) and the rows' (m, l); the list must provide both again
+    using carried_list = iro::util::type_list<iro::token::visible_at<axp::subject::in_tmem<O>, iro::scope::block>,
+                                              iro::token::alive<axp::subject::in_tmem<O>, iro::token::lifetime::block>,
+                                              iro::token::alive<State, iro::token::lifetime::warp>>;
 
     struct type : iro::compose::Composition<obligations, Cap, kThreads, kSoftmaxRegs> {
         using recipe = Recipe;
         using state = axp::state::SoftmaxStateF32;
+        using external = external_list;
+        using carried = carried_list;
         static constexpr int tile_q = TileQ, tile_k = TileK, head_dim = HeadDim, stages = Stages;
         static constexpr int kv_step = kKvStep, q_tiles = kQTilesPerCta, issuers = kIssuers;
         static constexpr int producer_regs = kProducerRegs, softmax_regs = kSoftmaxRegs;
@@ -91,6 +111,10 @@ struct AttentionTileTcgen05Impl {
         using schedule = typename AttentionTileTcgen05Impl::schedule;
     };
     static_assert(axp::kit::sm100::binds_all<obligations>::value, "every obligation needs an sm100 realization");
+    using flow = axp::graph::flow<obligations, external_list, carried_list>;
+    static_assert(flow::ports_complete, "a port of the sm100 attention graph lacks a token its payload needs");
+    static_assert(flow::first_unmet == -1, "an obligation of the sm100 attention graph requires a token that nothing before it provides");
+    static_assert(flow::carried_closed, "the KV step does not provide again what it takes from the previous step");
 };
 
 namespace registry {

@@ -10,6 +10,7 @@
 // rows to global memory.  KTiles is the window length; the runtime K loop and the
 // tile scheduler belong to the kernel.
 #pragma once
+#include "../graph/flow.hpp"
 #include "../kits/intent.hpp"
 #include "../kits/sm100/index.hpp"
 #include "../naming/subjects.hpp"
@@ -27,7 +28,7 @@ struct gemm_pipe_tag {
 
 template <class Recipe, int BlockM, int BlockN, int BlockK, int Stages, class ASubj, class BSubj, class CSubj, class Cap,
           class MemoryPatternA, class MemoryPatternB, class LoadModeA, class LoadModeB, class Schedule,
-          class EpiloguePolicy = epilogue::None>
+          class EpiloguePolicy = epilogue::None, class ScaleASubj = axp::subject::ScaleA, class ScaleBSubj = axp::subject::ScaleB>
 struct GemmTileTcgen05Impl {
     using in_a = typename Recipe::in_a;
     using in_b = typename Recipe::in_b;
@@ -68,43 +69,65 @@ struct GemmTileTcgen05Impl {
     static constexpr int kBBytes = BlockN / kCtaGroup * BlockK * in_b::bytes;
     static_assert(Stages * (kABytes + kBBytes) <= Cap::max_smem_bytes, "stage ring exceeds shared memory");
 
-    using mma = px::Tcgen05Mma<BlockM * kCtaGroup, BlockN, kMmaK, in_a, in_b, kCtaGroup>;
+    // wires: A and B travel global -> shared memory; the accumulator wire travels tensor memory -> registers, where the
+    // epilogue stages work on it in place; CSubj is the packed result, in registers and then in global memory
+    using Acc = axp::subject::Accumulator;
+    using mma = px::Tcgen05Mma<BlockM * kCtaGroup, BlockN, kMmaK, in_a, in_b, kCtaGroup, px::OperandSource::shared, px::Major::k, ASubj, BSubj, Acc>;
     using base = iro::util::type_list<
         px::HostMakeTensorMap<ASubj, in_a, 2>, px::HostMakeTensorMap<BSubj, in_b, 2>,
-        px::StageRing<ASubj, kABytes, Stages, 2>, px::StageRing<BSubj, kBBytes, Stages, 2>,
+        px::StageRing<ASubj, kABytes, Stages, 2, kCtaGroup>, px::StageRing<BSubj, kBBytes, Stages, 2, kCtaGroup>,
         px::RoleRegisterBudget<kProducerRegs, kEpilogueRegs>, px::TmemAllocate<kTmemCols, kCtaGroup>, px::BoundedBarrierWait, mma,
-        px::Tcgen05Commit<kCtaGroup>, px::TmemToRegisters<32>>;
-    using scale = std::conditional_t<Recipe::has_scales, iro::util::type_list<px::ScalePromoteAccumulator<Recipe>>,
+        px::Tcgen05Commit<kCtaGroup, Acc>, px::TmemToRegisters<32, Acc>>;
+    using scale = std::conditional_t<Recipe::has_scales, iro::util::type_list<px::ScalePromoteAccumulator<Recipe, Acc, ScaleASubj, ScaleBSubj>>,
                                      iro::util::type_list<>>;
+    using scale_external = std::conditional_t<Recipe::has_scales,
+                                              iro::util::concat_t<axp::graph::external_tokens<axp::subject::in_global<ScaleASubj>>,
+                                                                  axp::graph::external_tokens<axp::subject::in_global<ScaleBSubj>>>,
+                                              iro::util::type_list<>>;
     template <class P, bool = P::enabled>
     struct fused_list {
         using type = iro::util::type_list<>;
+        using external = iro::util::type_list<>;
     };
     template <class P, class = void>
     struct fused_one {
-        using type = px::BiasActivation<axp::subject::wire<typename P::bias_tag, 0>, typename P::activation>;
+        using bias = axp::subject::wire<typename P::bias_tag, 0>;
+        using type = px::BiasActivation<bias, typename P::activation, Acc>;
+        using external = axp::graph::external_tokens<axp::subject::in_global<bias>>;
     };
     template <class P>
     struct fused_one<P, std::void_t<typename P::up_tag>> {
         // a second tensor map for the up operand, then the gated combine
-        using type = px::GatedActivation<axp::subject::wire<typename P::up_tag, 0>, typename P::activation>;
+        using type = px::GatedActivation<axp::subject::wire<typename P::up_tag, 0>, typename P::activation, Acc>;
+        using external = iro::util::type_list<>;
     };
     template <class P>
     struct fused_one<P, std::void_t<typename P::c_tag>> {
-        using type = px::LinearCombination<axp::subject::wire<typename P::c_tag, 0>, axp::subject::wire<typename P::alpha_tag, 0>,
-                                           axp::subject::wire<typename P::beta_tag, 0>>;
+        using c = axp::subject::wire<typename P::c_tag, 0>;
+        using alpha = axp::subject::wire<typename P::alpha_tag, 0>;
+        using beta = axp::subject::wire<typename P::beta_tag, 0>;
+        using type = px::LinearCombination<c, alpha, beta, Acc>;
+        using external = iro::util::concat_t<axp::graph::external_tokens<axp::subject::in_global<c>>,
+                                             iro::util::concat_t<axp::graph::external_tokens<alpha>, axp::graph::external_tokens<beta>>>;
     };
     template <class P>
     struct fused_list<P, true> {
         using type = iro::util::type_list<typename fused_one<P>::type>;
+        using external = typename fused_one<P>::external;
     };
     using fused = typename fused_list<EpiloguePolicy>::type;
-    using tail = iro::util::type_list<px::CastPack<iro::elem::f32, out, typename Recipe::fp8_policy>,
-                                      px::StoreRowGlobal<out>, px::TmemRelease<kTmemCols, kCtaGroup>>;
+    using tail = iro::util::type_list<px::CastPack<iro::elem::f32, out, typename Recipe::fp8_policy, Acc, CSubj>,
+                                      px::StoreRowGlobal<out, CSubj>, px::TmemRelease<kTmemCols, kCtaGroup>>;
     using obligations = iro::util::concat_t<iro::util::concat_t<iro::util::concat_t<base, scale>, fused>, tail>;
+    // what the caller hands over: the operands (and scales, bias, C, alpha, beta where the recipe reads them)
+    using external_list = iro::util::concat_t<
+        iro::util::concat_t<axp::graph::external_tokens<axp::subject::in_global<ASubj>>, axp::graph::external_tokens<axp::subject::in_global<BSubj>>>,
+        iro::util::concat_t<scale_external, typename fused_list<EpiloguePolicy>::external>>;
 
     struct type : iro::compose::Composition<obligations, Cap, kThreads, 232> {
         using recipe = Recipe;
+        using external = external_list;
+        using carried = iro::util::type_list<>;      // a tile's pipeline starts from nothing: no loop-carried tokens
         static constexpr int block_m = BlockM, block_n = BlockN, block_k = BlockK, stages = Stages;
         static constexpr int cta_group = kCtaGroup, producer_regs = kProducerRegs, epilogue_regs = kEpilogueRegs;
         using a_swizzle = typename GemmTileTcgen05Impl::a_swizzle;
@@ -116,6 +139,9 @@ struct GemmTileTcgen05Impl {
         static constexpr bool fused_epilogue = EpiloguePolicy::enabled;
     };
     static_assert(axp::kit::sm100::binds_all<obligations>::value, "every obligation needs an sm100 realization");
+    using flow = axp::graph::flow<obligations, external_list>;
+    static_assert(flow::ports_complete, "a port of the sm100 GEMM graph lacks a token its payload needs");
+    static_assert(flow::first_unmet == -1, "an obligation of the sm100 GEMM graph requires a token that nothing before it provides");
 };
 
 namespace registry {
@@ -126,7 +152,8 @@ template <class Recipe, int BM, int BN, int BK, int Stages, int KTiles, class AS
 struct resolve_impl<GemmTilePattern<Recipe, BM, BN, BK, Stages, KTiles, ASubj, BSubj, CSubj, WgmmaSubj, MPA, MPB, LMA, LMB,
                                     Schedule, ScaleASubj, ScaleBSubj, ATma, BTma>,
                     Cap, std::enable_if_t<Cap::has_tcgen05>> {
-    using type = typename GemmTileTcgen05Impl<Recipe, BM, BN, BK, Stages, ASubj, BSubj, CSubj, Cap, MPA, MPB, LMA, LMB, Schedule>::type;
+    using type = typename GemmTileTcgen05Impl<Recipe, BM, BN, BK, Stages, ASubj, BSubj, CSubj, Cap, MPA, MPB, LMA, LMB, Schedule, epilogue::None,
+                                              ScaleASubj, ScaleBSubj>::type;
 };
 
 template <class Recipe, int BM, int BN, int BK, int Stages, int KTiles, class ASubj, class BSubj, class CSubj, class WgmmaSubj,
@@ -135,7 +162,8 @@ template <class Recipe, int BM, int BN, int BK, int Stages, int KTiles, class AS
 struct resolve_impl<GemmTileFusedPattern<Recipe, BM, BN, BK, Stages, KTiles, ASubj, BSubj, CSubj, WgmmaSubj, Epi, MPA, MPB, LMA,
                                          LMB, Schedule, ScaleASubj, ScaleBSubj, ATma, BTma>,
                     Cap, std::enable_if_t<Cap::has_tcgen05>> {
-    using type = typename GemmTileTcgen05Impl<Recipe, BM, BN, BK, Stages, ASubj, BSubj, CSubj, Cap, MPA, MPB, LMA, LMB, Schedule, Epi>::type;
+    using type = typename GemmTileTcgen05Impl<Recipe, BM, BN, BK, Stages, ASubj, BSubj, CSubj, Cap, MPA, MPB, LMA, LMB, Schedule, Epi, ScaleASubj,
+                                              ScaleBSubj>::type;
 };
 
 }  // namespace registry

@@ -19,5 +19,6 @@ AXP_TAG(P);
 AXP_TAG(ScaleA);
 AXP_TAG(ScaleB);
 AXP_TAG(Lse);
+AXP_TAG(State);
 #undef AXP_TAG
 }  // namespace axp::tag

@@ -193,8 +193,172 @@ struct sm100 {
 
 }  // namespace iro::cap
 
+// ------------------------------------------------------- scopes, executors, tokens ----
+// The typestate vocabulary of the contracts (reference core: execution groups :763-820, scopes :822-889, token
+// families :937-1210, token queries :1458-1650, payload concepts :2566-2590, ports :2949-3010), restated for what the sm100 graphs need: three token
+// families (visible_at, alive, sync_at), ordered scopes and lifetimes, and input / output ports that carry them.
+namespace iro::scope {
+#define IRO_SCOPE(name, lvl)                                                                  \
+    struct name {                                                                             \
+        static constexpr int level = lvl;                                                     \
+        static constexpr iro::util::u64 id = iro::util::fnv1a_64_cstr("iro.scope." #name);    \
+    }
+IRO_SCOPE(lane, 0);
+IRO_SCOPE(warp, 1);
+IRO_SCOPE(warpgroup, 2);
+IRO_SCOPE(block, 3);
+IRO_SCOPE(cluster, 4);
+IRO_SCOPE(device, 5);
+#undef IRO_SCOPE
+}  // namespace iro::scope
+
+namespace iro::exec {
+// Who executes an obligation; `scope` is the smallest scope that contains all of its threads.
+#define IRO_EXEC(name, scope_name)                                                            \
+    struct name {                                                                             \
+        using scope = iro::scope::scope_name;                                                 \
+        static constexpr iro::util::u64 id = iro::util::fnv1a_64_cstr("iro.exec." #name);     \
+    }
+IRO_EXEC(lane, lane);              // one elected thread (TMA issue, tcgen05.mma, tcgen05.commit)
+IRO_EXEC(warp, warp);
+IRO_EXEC(warpgroup, warpgroup);
+IRO_EXEC(block, block);
+IRO_EXEC(cta_group1, block);       // tensor-core work of one CTA
+IRO_EXEC(cta_group2, cluster);     // tensor-core work of a CTA pair
+IRO_EXEC(host, device);
+#undef IRO_EXEC
+}  // namespace iro::exec
+
+namespace iro::scope {
+template <class Exec>
+using min_scope_for_t = typename Exec::scope;
+}  // namespace iro::scope
+
+namespace iro::token {
+
+struct kind_visible_at { static constexpr auto id = iro::util::fnv1a_64_cstr("iro.token.kind_visible_at"); };
+struct kind_alive { static constexpr auto id = iro::util::fnv1a_64_cstr("iro.token.kind_alive"); };
+struct kind_sync_at { static constexpr auto id = iro::util::fnv1a_64_cstr("iro.token.kind_sync_at"); };
+
+namespace lifetime {
+#define IRO_LIFETIME(name, lvl)                                                                 \
+    struct name {                                                                               \
+        static constexpr int level = lvl;                                                       \
+        static constexpr iro::util::u64 id = iro::util::fnv1a_64_cstr("iro.lifetime." #name);   \
+    }
+IRO_LIFETIME(instruction, 0);
+IRO_LIFETIME(warp, 1);
+IRO_LIFETIME(warpgroup, 2);
+IRO_LIFETIME(block, 3);
+IRO_LIFETIME(cluster, 4);
+IRO_LIFETIME(kernel, 5);
+#undef IRO_LIFETIME
+}  // namespace lifetime
+
+// The subject's contents can be read by every thread of `Scope` (and, for async-proxy consumers, by the units that act
+// for them).
+template <class Subject, class Scope>
+struct visible_at {
+    using kind = kind_visible_at;
+    using subject = Subject;
+    using scope = Scope;
+    static constexpr int level = Scope::level;
+    static constexpr iro::util::u64 id =
+        iro::util::mix_u64(iro::util::fnv1a_64_cstr("iro.token.visible_at"), iro::util::mix_u64(Subject::id, Scope::id));
+};
+// The subject's storage stays allocated for `Lifetime`.
+template <class Subject, class Lifetime>
+struct alive {
+    using kind = kind_alive;
+    using subject = Subject;
+    using lifetime = Lifetime;
+    static constexpr int level = Lifetime::level;
+    static constexpr iro::util::u64 id =
+        iro::util::mix_u64(iro::util::fnv1a_64_cstr("iro.token.alive"), iro::util::mix_u64(Subject::id, Lifetime::id));
+};
+// A synchronisation of `Scope` (barrier, mbarrier phase, commit) orders the producer of the subject before its readers.
+template <class Subject, class Scope>
+struct sync_at {
+    using kind = kind_sync_at;
+    using subject = Subject;
+    using scope = Scope;
+    static constexpr int level = Scope::level;
+    static constexpr iro::util::u64 id =
+        iro::util::mix_u64(iro::util::fnv1a_64_cstr("iro.token.sync_at"), iro::util::mix_u64(Subject::id, Scope::id));
+};
+
+}  // namespace iro::token
+
+namespace iro::verify {
+
+// Does `Tokens` hold a token of this kind for this subject (any scope / lifetime)?
+template <class Tokens, class Kind, class Subject>
+struct has_token_kind_subject_impl;
+template <class Kind, class Subject, class... Ts>
+struct has_token_kind_subject_impl<iro::util::type_list<Ts...>, Kind, Subject>
+    : std::bool_constant<((std::is_same_v<typename Ts::kind, Kind> && std::is_same_v<typename Ts::subject, Subject>) || ...)> {};
+template <class Tokens, class Kind, class Subject>
+constexpr bool has_token_kind_subject() {
+    return has_token_kind_subject_impl<Tokens, Kind, Subject>::value;
+}
+
+// Does `Provided` satisfy the token `Need`: same kind and subject, at a scope / lifetime at least as wide?
+template <class Provided, class Need>
+struct satisfies_impl;
+template <class Need, class... Ts>
+struct satisfies_impl<iro::util::type_list<Ts...>, Need>
+    : std::bool_constant<((std::is_same_v<typename Ts::kind, typename Need::kind> &&
+                           std::is_same_v<typename Ts::subject, typename Need::subject> && Ts::level >= Need::level) || ...)> {};
+template <class Provided, class Need>
+inline constexpr bool satisfies_v = satisfies_impl<Provided, Need>::value;
+
+}  // namespace iro::verify
+
 // ------------------------------------------------- obligations / realizations ----
 namespace iro::contract {
+
+// What a port carries (reference core: payload concepts :2566-2590).
+namespace space {
+struct global { static constexpr auto id = iro::util::fnv1a_64_cstr("iro.space.global"); };
+struct shared { static constexpr auto id = iro::util::fnv1a_64_cstr("iro.space.shared"); };
+struct tmem { static constexpr auto id = iro::util::fnv1a_64_cstr("iro.space.tmem"); };
+struct reg { static constexpr auto id = iro::util::fnv1a_64_cstr("iro.space.reg"); };
+}  // namespace space
+struct tile_kind {};
+struct handle_kind {};
+struct scalar_kind {};
+// A tile of data in a memory space.
+template <class Space>
+struct Tile {
+    using payload_kind = tile_kind;
+    using space = Space;
+};
+// An opaque handle: tensor map, mbarrier, tensor-memory base address, matrix descriptor.
+struct Handle { using payload_kind = handle_kind; };
+// A per-thread or per-call value (scales alpha / beta, softmax state).
+struct Scalar { using payload_kind = scalar_kind; };
+template <class P>
+concept TilePayload = std::is_same_v<typename P::payload_kind, tile_kind>;
+template <class P>
+concept HandlePayload = std::is_same_v<typename P::payload_kind, handle_kind>;
+
+// Ports: what an obligation needs to hold before it runs (`required`) and what holds after it (`provided`).
+template <class Payload, class Subject, class ExecGroup, class Required>
+struct InputPort {
+    static constexpr bool is_input = true;
+    using payload = Payload;
+    using subject = Subject;
+    using exec_group = ExecGroup;
+    using required = Required;
+};
+template <class Payload, class Subject, class ExecGroup, class Provided>
+struct OutputPort {
+    static constexpr bool is_input = false;
+    using payload = Payload;
+    using subject = Subject;
+    using exec_group = ExecGroup;
+    using provided = Provided;
+};
 
 namespace subject {
 struct global { static constexpr iro::util::u64 id = iro::util::fnv1a_64_cstr("iro.subject.global"); };
@@ -213,6 +377,9 @@ template <iro::util::u64 Id, class Res = Resources<>>
 struct Obligation {
     static constexpr iro::util::u64 id = Id;
     using resources = Res;
+    // Ports; an obligation that moves or makes data overrides them.
+    using inputs = iro::util::type_list<>;
+    using outputs = iro::util::type_list<>;
 };
 
 // Base of every realization (reference core:3290-3300): the id mixes the obligation's id with the implementation id,

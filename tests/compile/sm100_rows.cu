@@ -161,6 +161,107 @@ static_assert(!axp::kit::sm100::detail::has_execute<NoExecuteProbe>::value);
 static_assert(iro::util::contains<axp::realize::sm100::Tcgen05Mma<1, false>, axp::kit::sm100::bind<MmaFp8>::realization::leaves>::value);
 static_assert(axp::kit::sm100::bind<px::BoundedBarrierWait>::found);
 
+// ---- tokens, ports and contract flow ---------------------------------------------------
+// (reference: contract_tokens_complete pins Tcgen05Mma and the tensor-memory moves,
+// tests/compile/ax_asserts_primitives.cu:146-155,571-576; rules in include/axp/protocol/audit/tokens.hpp:35-80)
+namespace flowtest {
+namespace sj = axp::subject;
+namespace tk = iro::token;
+namespace audit = axp::protocol::audit;
+using iro::util::type_list;
+using Acc = sj::Accumulator;
+using e4 = iro::elem::e4m3;
+using b16 = iro::elem::bf16;
+
+// every obligation kind of the two graphs names complete token lists on its ports
+using MmaPair = px::Tcgen05Mma<256, 256, 32, e4, e4, 2, px::OperandSource::shared, px::Major::k, sj::MatrixA, sj::MatrixB, Acc>;
+using MmaOne = px::Tcgen05Mma<128, 256, 32, e4, e4, 1, px::OperandSource::shared, px::Major::k, sj::MatrixA, sj::MatrixB, Acc>;
+using MmaTs = px::Tcgen05Mma<128, 128, 16, b16, b16, 1, px::OperandSource::tmem, px::Major::mn, sj::AttentionP, sj::AttentionV, sj::Output>;
+static_assert(audit::contract_tokens_complete<MmaPair>() && audit::contract_tokens_complete<MmaOne>() && audit::contract_tokens_complete<MmaTs>());
+static_assert(audit::contract_tokens_complete<px::Tcgen05Commit<2, Acc>>() && audit::contract_tokens_complete<px::TmemToRegisters<32, Acc>>() &&
+              audit::contract_tokens_complete<px::RegistersToTmem<32, sj::AttentionP>>() &&
+              audit::contract_tokens_complete<px::RegistersToSharedOperand<16384, 4, sj::AttentionP>>());
+static_assert(audit::contract_tokens_complete<px::HostMakeTensorMap<sj::MatrixA, e4, 2>>() &&
+              audit::contract_tokens_complete<px::StageRing<sj::MatrixA, 16384, 6, 2, 2>>() && audit::contract_tokens_complete<px::TmemAllocate<512, 2>>() &&
+              audit::contract_tokens_complete<px::TmemRelease<512, 2>>() && audit::contract_tokens_complete<px::BoundedBarrierWait>());
+static_assert(audit::contract_tokens_complete<px::ScalePromoteAccumulator<axp::recipe::E4M3BlockScaledAccF32OutBF16>>() &&
+              audit::contract_tokens_complete<px::CastPack<iro::elem::f32, b16, iro::recipe::fp8_native>>() &&
+              audit::contract_tokens_complete<px::StoreRowGlobal<b16>>() && audit::contract_tokens_complete<px::CausalMaskPredicate<128, 64>>() &&
+              audit::contract_tokens_complete<px::RowSoftmaxStateUpdate>() && audit::contract_tokens_complete<px::RescaleAccumulatorInTmem>() &&
+              audit::contract_tokens_complete<px::CastWeights<b16, iro::recipe::fp8_native>>());
+// the operands of a pair MMA must be published at cluster scope, its result is visible to the issuing lane only
+using PairA = iro::util::front_t<MmaPair::inputs>;
+static_assert(PairA::is_input && std::is_same_v<PairA::subject, sj::in_shared<sj::MatrixA>> && std::is_same_v<PairA::exec_group, iro::exec::cta_group2>);
+static_assert(iro::verify::has_token_kind_subject<PairA::required, tk::kind_sync_at, sj::in_shared<sj::MatrixA>>());
+static_assert(std::is_same_v<iro::util::front_t<iro::util::front_t<MmaPair::outputs>::provided>, tk::visible_at<sj::in_tmem<Acc>, iro::scope::lane>>);
+// the audit rejects incomplete ports: a tile without liveness; a block-wide output without its synchronisation
+using NoAlive = iro::contract::InputPort<iro::contract::Tile<iro::contract::space::shared>, sj::in_shared<sj::MatrixA>, iro::exec::warp,
+                                         type_list<tk::visible_at<sj::in_shared<sj::MatrixA>, iro::scope::warp>>>;
+using NoSync = iro::contract::OutputPort<iro::contract::Tile<iro::contract::space::tmem>, sj::in_tmem<Acc>, iro::exec::cta_group1,
+                                         type_list<tk::visible_at<sj::in_tmem<Acc>, iro::scope::block>, tk::alive<sj::in_tmem<Acc>, tk::lifetime::block>>>;
+using LaneOut = iro::contract::OutputPort<iro::contract::Tile<iro::contract::space::tmem>, sj::in_tmem<Acc>, iro::exec::lane,
+                                          type_list<tk::visible_at<sj::in_tmem<Acc>, iro::scope::lane>, tk::alive<sj::in_tmem<Acc>, tk::lifetime::block>>>;
+static_assert(!audit::port_tokens_complete<NoAlive>() && !audit::port_tokens_complete<NoSync>() && audit::port_tokens_complete<LaneOut>());
+// satisfies: same kind and subject at a scope at least as wide
+static_assert(iro::verify::satisfies_v<type_list<tk::visible_at<Acc, iro::scope::block>>, tk::visible_at<Acc, iro::scope::warp>>);
+static_assert(!iro::verify::satisfies_v<type_list<tk::visible_at<Acc, iro::scope::lane>>, tk::visible_at<Acc, iro::scope::warp>>);
+static_assert(!iro::verify::satisfies_v<type_list<tk::visible_at<sj::Output, iro::scope::block>>, tk::visible_at<Acc, iro::scope::warp>>);
+
+// flow over hand-made lists: the GEMM chain closes; taking a link out names the obligation that is left without its token
+using Ext = iro::util::concat_t<axp::graph::external_tokens<sj::in_global<sj::MatrixA>>, axp::graph::external_tokens<sj::in_global<sj::MatrixB>>>;
+using Good = type_list<px::HostMakeTensorMap<sj::MatrixA, e4, 2>, px::HostMakeTensorMap<sj::MatrixB, e4, 2>, px::StageRing<sj::MatrixA, 16384, 6, 2, 2>,
+                       px::StageRing<sj::MatrixB, 16384, 6, 2, 2>, px::TmemAllocate<512, 2>, MmaPair, px::Tcgen05Commit<2, Acc>,
+                       px::TmemToRegisters<32, Acc>, px::CastPack<iro::elem::f32, b16, iro::recipe::fp8_native, Acc, sj::MatrixC>,
+                       px::StoreRowGlobal<b16, sj::MatrixC>, px::TmemRelease<512, 2>>;
+static_assert(axp::graph::flow<Good, Ext>::closed);
+// no tcgen05.commit between the MMA and the tensor-memory read: the read (index 6) has nothing that published the accumulator
+using NoCommit = type_list<px::HostMakeTensorMap<sj::MatrixA, e4, 2>, px::HostMakeTensorMap<sj::MatrixB, e4, 2>, px::StageRing<sj::MatrixA, 16384, 6, 2, 2>,
+                           px::StageRing<sj::MatrixB, 16384, 6, 2, 2>, px::TmemAllocate<512, 2>, MmaPair, px::TmemToRegisters<32, Acc>>;
+static_assert(axp::graph::flow<NoCommit, Ext>::first_unmet == 6);
+// B never staged: the MMA (index 4) lacks its operand
+using NoRingB = type_list<px::HostMakeTensorMap<sj::MatrixA, e4, 2>, px::HostMakeTensorMap<sj::MatrixB, e4, 2>, px::StageRing<sj::MatrixA, 16384, 6, 2, 2>,
+                          px::TmemAllocate<512, 2>, MmaPair>;
+static_assert(axp::graph::flow<NoRingB, Ext>::first_unmet == 4);
+// rings filled per CTA feeding a pair MMA: published at block scope, required at cluster scope
+using BlockRings = type_list<px::HostMakeTensorMap<sj::MatrixA, e4, 2>, px::HostMakeTensorMap<sj::MatrixB, e4, 2>, px::StageRing<sj::MatrixA, 16384, 6, 2, 1>,
+                             px::StageRing<sj::MatrixB, 16384, 6, 2, 1>, px::TmemAllocate<512, 2>, MmaPair>;
+static_assert(axp::graph::flow<BlockRings, Ext>::first_unmet == 5);
+// no tensor map: the ring (index 0) cannot issue its copies; no tensor-memory allocation: the MMA cannot name its accumulator
+static_assert(axp::graph::flow<type_list<px::StageRing<sj::MatrixA, 16384, 6, 2, 2>>, Ext>::first_unmet == 0);
+using NoAlloc = type_list<px::HostMakeTensorMap<sj::MatrixA, e4, 2>, px::HostMakeTensorMap<sj::MatrixB, e4, 2>, px::StageRing<sj::MatrixA, 16384, 6, 2, 2>,
+                          px::StageRing<sj::MatrixB, 16384, 6, 2, 2>, MmaPair>;
+static_assert(axp::graph::flow<NoAlloc, Ext>::first_unmet == 4);
+// an operand nobody handed to the kernel
+static_assert(axp::graph::flow<Good, axp::graph::external_tokens<sj::in_global<sj::MatrixA>>>::first_unmet == 1);
+
+// loop-carried tokens: a KV step that takes the published accumulator from the previous step must publish it again
+using O = sj::Output;
+using CarriedO = type_list<tk::visible_at<sj::in_tmem<O>, iro::scope::block>, tk::alive<sj::in_tmem<O>, tk::lifetime::block>>;
+using StepOpen = type_list<px::TmemAllocate<512, 1>, px::RescaleAccumulatorInTmemOn<O, sj::SoftmaxState>>;
+using CarriedState = iro::util::concat_t<CarriedO, type_list<tk::alive<sj::SoftmaxState, tk::lifetime::warp>>>;
+static_assert(axp::graph::flow<StepOpen, type_list<>, CarriedState>::first_unmet == -1);
+static_assert(!axp::graph::flow<StepOpen, type_list<>, CarriedState>::carried_closed, "the state is taken and never provided again");
+
+// the shipped graphs: closed, and every row's graph passes verify (which includes the flow)
+template <class Preset>
+constexpr bool graph_flow_closed() {
+    using G = Graph<Preset>;
+    using F = axp::graph::flow<typename G::obligations, typename G::external, typename G::carried>;
+    return F::ports_complete && F::first_unmet == -1 && F::carried_closed && axp::graph::flow_closed<G>();
+}
+static_assert(graph_flow_closed<preset::GemmFp8BlockScaled128x256x128>() && graph_flow_closed<preset::GemmBf16_128x256x64>() &&
+              graph_flow_closed<preset::GemmBf16_128x256x64BiasSiLU>() && graph_flow_closed<preset::GemmBf16_128x256x64SwiGLU>() &&
+              graph_flow_closed<preset::GemmBf16_128x256x64LinComb>() && graph_flow_closed<preset::Attention128x128x128CausalBf16>() &&
+              graph_flow_closed<preset::Attention128x128x128CausalFp8Gqa>());
+// the attention step carries the accumulator and the row state; the GEMM carries nothing
+static_assert(Graph<preset::Attention128x128x128CausalBf16>::carried::size == 3 && Graph<preset::GemmBf16_128x256x64>::carried::size == 0);
+// the E4M3 attention routes P through shared memory, the bf16 one through tensor memory: the P.V MMA's A port follows
+using AttnF8 = Graph<preset::Attention128x128x128CausalFp8Gqa>;
+using AttnBf = Graph<preset::Attention128x128x128CausalBf16>;
+static_assert(iro::util::contains<px::RegistersToSharedOperand<16384, 4, sj::AttentionP>, AttnF8::obligations>::value);
+static_assert(iro::util::contains<px::RegistersToTmem<32, sj::AttentionP>, AttnBf::obligations>::value);
+}  // namespace flowtest
+
 // ---- not realised on sm100 ----------------------------------------------------------
 using F16Gemm = axp::level3::registry::GemmTilePattern<axp::recipe::F16AccF32Fast, 128, 256, 48, 4, 5, preset::GemmA, preset::GemmB,
                                                        preset::GemmC, preset::GemmAcc, axp::intent::memory_pattern::Optimized,
