@@ -750,7 +750,7 @@ def measure(ctx, wl, steps, warmup):
     ctx.pkg.ops.check_status(ctx.dev)
     per_launch = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(steps))
     total_ms = ctx.max_over_ranks(evs[0].elapsed_time(evs[-1]))
-    return {"ms_per_step": total_ms / steps, "kernel_ms": sum(per_launch) / len(per_launch), "kernel_ms_min": per_launch[0],
+    return {"ms_per_step": total_ms / steps, "kernel_ms": sum(per_launch) / len(per_launch), "kernel_ms_min": per_launch[0], "kernel_ms_median": per_launch[len(per_launch) // 2],
             "clocks": sampler.result(), "timed_s": total_ms * 1e-3}
 
 
@@ -767,7 +767,7 @@ def roofline(ctx, wl, key, m):
         peak = peaks["hbm_gbs"]
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                 "peak_source": f"{loud}{peaks['source']} STREAM-style copy {peak} GB/s", "kernel_ms": m["kernel_ms"],
-                "kernel_ms_min": m["kernel_ms_min"], "hbm_min_bytes": wl.bytes_min}
+                "kernel_ms_min": m["kernel_ms_min"], "kernel_ms_median": m["kernel_ms_median"], "hbm_min_bytes": wl.bytes_min}
     burst = m["timed_s"] < 1.0
     bf16_peak = peaks["bf16_burst"] if burst else peaks["bf16_sustained"]
     eight_bit = wl.dtype == "e4m3"
@@ -778,7 +778,7 @@ def roofline(ctx, wl, key, m):
                             f"(timed region {m['timed_s'] * 1e3:.1f} ms {'<' if burst else '>='} 1 s)"
                             + (", x2 for the 8-bit tensor rate: no E4M3 figure is measured there" if eight_bit else "")),
             "frac_of_nominal": achieved / NOMINAL_TFLOPS[wl.dtype], "nominal_peak": NOMINAL_TFLOPS[wl.dtype],
-            "kernel_ms": m["kernel_ms"], "kernel_ms_min": m["kernel_ms_min"], "hbm_min_bytes": wl.bytes_min,
+            "kernel_ms": m["kernel_ms"], "kernel_ms_min": m["kernel_ms_min"], "kernel_ms_median": m["kernel_ms_median"], "hbm_min_bytes": wl.bytes_min,
             "hbm_gbs_at_min_bytes": wl.bytes_min / (m["kernel_ms"] * 1e-3) / 1e9}
 
 
