@@ -139,7 +139,7 @@ class GemmFp8(Workload):
 
 
 class GemmFp8Strong(Workload):
-    """cfg1 as BASELINE.json words it for N GPUs: ONE 8192^3 problem whose output columns are split over the ranks
+    """cfg1 as the benchmark configuration words it for N GPUs: ONE 8192^3 problem whose output columns are split over the ranks
     (boundaries at multiples of 256); A and sA replicated, no collective unless the full C is asked for."""
     dtype = "e4m3"
     scaling = "strong"
