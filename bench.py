@@ -16,7 +16,8 @@ The default run also times, in the same process, the other workloads of the metr
 of at least two seconds ("sustained") and one library E4M3 GEMM as a reference point ("library_reference").
 
 Other workloads (--workload): gemm_fp8_strong, gemm_bf16_gate_up, gemm_bf16_down, gemm_bf16_swiglu, gemm_fp8_swiglu,
-attn_bf16, attn_fp8, quantize_fp8, rmsnorm_quantize_fp8, attn_decode_bf16, attn_decode_fp8.
+attn_bf16, attn_fp8, quantize_fp8, rmsnorm_quantize_fp8, attn_decode_bf16, attn_decode_fp8; attn_ring (two or more GPUs:
+ring attention over one sequence sharded by position, device timing only).
 
 `--impl reference` times the CPU host oracle (the reference library has no
 runnable implementation of this path) on the box's host cores, on a bounded row
@@ -540,7 +541,47 @@ class AttnDecodeFp8(Workload):
         return (lambda: oracle.attn_fwd_fp8(q, k, v, a, b, c, self.scale, True, q_range=(self.Skv - 1, self.Skv))), float(self.bytes_min) / self.B
 
 
+class AttnRing(Workload):
+    """Ring attention over the GPUs of the box (opt-in: --workload attn_ring with --gpus >= 2): ONE causal sequence of
+    8192 positions per GPU, queries and keys sharded by position, K / V shards passed round by NCCL point-to-point sends
+    while the pass over the shard in hand runs.  Under the causal mask rank r runs r + 1 of the N passes, so the last
+    rank sets the time: the figure shows what the unbalanced ring delivers, not a balanced one."""
+    dtype = "bf16"
+    scaling = "strong"
+    no_host_arms = "the shards live on the GPUs of a sequence-parallel job: no host-buffer arm and no CPU sample for this workload"
+    sharding_note = ("one sequence sharded by position (queries, keys and values alike); per call every rank sends its K / V shard once round the "
+                     "ring (NCCL point-to-point) and merges one partial result per shard; causal: rank r runs r + 1 of the N passes")
+    B, Hq, Hkv, D, S_PER_GPU = 1, 32, 8, 128, 8192
+
+    def __init__(self, pkg, dev, rank, world, sets=2):
+        super().__init__(pkg, dev, rank, world)
+        self.S = self.S_PER_GPU * world
+        self.name = (f"ring attention: bf16 causal, B=1 Hq=32 Hkv=8 D=128, ONE sequence of {self.S} positions sharded by position over "
+                     f"{world} GPUs (8192 per GPU), K/V shards passed round a ring")
+        p0, p1 = pkg.shard.kv_shard_range(self.S, world, rank)
+        self.job_flops = 0.5 * 4.0 * self.B * self.Hq * float(self.S) * self.S * self.D
+        passes = sum(1 for st in pkg.shard.ring_shard_plan(self.S, world, rank, True) if st[4])
+        self.flops = self.job_flops / world      # the job's work per GPU: the ring is not balanced, rank r does (r + 1/2) / (N^2 / 2) of it
+        self.bytes_min = 0
+        self.launches_per_step = passes + 1
+        self.kv_bytes_per_step = 2 * self.B * self.Hkv * self.S_PER_GPU * self.D * 2 * (world - 1)         # sent by this rank per call
+        self.sets = []
+        for s in range(sets):
+            # every rank draws its own shard (the values do not matter for the timing; parity is the tests' business)
+            Q, _, _, self.scale = pkg.synth.bf16_attention_inputs(self.B, self.Hq, p1 - p0, self.D, seed=100 * s + rank, Hkv=self.Hkv, device=dev)
+            _, K, V, _ = pkg.synth.bf16_attention_inputs(self.B, self.Hkv, p1 - p0, self.D, seed=100 * s + rank + 50, device=dev)
+            self.sets.append((Q, K, V))
+
+    def step(self, i):
+        Q, K, V = self.sets[i % len(self.sets)]
+        self.out = self.pkg.shard.attn_ring(Q, K, V, self.scale, True, self.S, self.world, self.rank)
+
+
 def make_workload(name, pkg, dev, rank, world):
+    if name == "attn_ring":
+        if world < 2:
+            raise SystemExit("attn_ring needs --gpus >= 2 (one process per GPU under torchrun)")
+        return AttnRing(pkg, dev, rank, world)
     if name == "gemm_fp8":
         return GemmFp8(pkg, dev, rank, world)
     if name == "gemm_fp8_strong":
@@ -649,9 +690,9 @@ def cpu_baseline(wl, budget_s=12.0):
 def config_for(wl, world):
     """The `config` object both arms print (identical keys and wording)."""
     return {"workload": wl.name,
-            "sharding": ("single GPU" if world == 1 else
+            "sharding": (getattr(wl, "sharding_note", None) or ("single GPU" if world == 1 else
                          "headline workload: every rank runs the named shape on its own output-column shard of a world-times wider problem "
-                         "(weak scaling, no data-path collective); attention sub-records split the ONE named problem by heads (strong)"),
+                         "(weak scaling, no data-path collective); attention sub-records split the ONE named problem by heads (strong)")),
             "l2": "two operand sets alternate between steps; each set (>= 130 MB per rank) exceeds the 126 MB L2",
             "timing": "GPU arm: CUDA events on the launch stream, max over ranks; reference arm: host wall clock of the CPU oracle"}
 
@@ -903,7 +944,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="gemm_fp8",
-                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8"])
+                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8", "attn_ring"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -953,7 +994,10 @@ def main():
     extras = args.workload == "gemm_fp8" and not args.no_extra
 
     # ---- end to end: host buffers in, host result out, every step ------------------
-    if not args.no_e2e:
+    if getattr(wl, "no_host_arms", None):
+        line["e2e_note"] = wl.no_host_arms
+        line["ring"] = {"kv_bytes_sent_per_gpu_per_call": wl.kv_bytes_per_step, "passes_on_this_rank": wl.launches_per_step - 1}
+    elif not args.no_e2e:
         line["e2e"] = e2e_record(ctx, wl, max(4, min(args.steps, 24)))
 
     # ---- the other workloads of the metric, same process (sub-records) -------------
@@ -982,7 +1026,7 @@ def main():
         wl = make_workload(args.workload, pkg, dev, rank, world)
         line["sustained"] = sustained_record(ctx, wl, m["ms_per_step"])
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not getattr(wl, "no_host_arms", None):
             line["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(line))
     if world > 1:

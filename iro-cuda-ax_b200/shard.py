@@ -7,6 +7,9 @@
   the full C, which is then an all-gather of the column shards.
 * Attention: flattened batch x head (bf16) or batch x KV-head group (fp8 GQA) is
   split into contiguous ranges; no collective.
+* Long sequences (sequence / context parallelism): ``attn_kv_sharded`` shards the keys (every rank holds all
+  queries; one all-gather of partial results), ``attn_ring`` shards queries and keys alike and passes the K / V
+  shards round a ring (point-to-point exchange overlapped with the pass over the shard in hand).
 """
 from __future__ import annotations
 
@@ -94,6 +97,87 @@ def attn_kv_sharded(Q, K_local, V_local, scale: float, causal: bool, skv_total: 
     gathered = torch.empty((world, part.numel()), dtype=torch.uint8, device=part.device)
     dist.all_gather_into_tensor(gathered, part.view(1, -1), group=group)
     return combine_fn(gathered, tuple(Q.shape))
+
+
+def ring_shard_plan(s_total: int, world: int, rank: int, causal: bool):
+    """What rank `rank` does in each of the `world` steps of ``attn_ring``: a list of
+    ``(k_rank, (k0, k1), kv_pos0, skv_total_arg, run)`` - the rank whose K / V shard is in hand at that step, its key
+    range, and the two position arguments of ``axp_sm100_attn_fwd_bf16_kvshard`` for the local queries [q0, q1)
+    against it; ``run`` is False when the pass is skipped (no keys, no queries, or - under the causal mask - a shard
+    that lies wholly in the future of every local query).
+
+    Under the causal mask local query i (global position q0 + i) sees global keys <= q0 + i.  The entry point's rule
+    is "query i sees keys <= i + (skv_total - Sq)", so the call passes skv_total = q1: the sequence as far as this
+    rank's last query."""
+    q0, q1 = kv_shard_range(s_total, world, rank)
+    plan = []
+    for t in range(world):
+        k_rank = (rank - t) % world
+        k0, k1 = kv_shard_range(s_total, world, k_rank)
+        run = k1 > k0 and q1 > q0 and not (causal and k0 >= q1)
+        plan.append((k_rank, (k0, k1), k0, q1 if causal else s_total, run))
+    return plan
+
+
+def attn_ring(Q_local, K_local, V_local, scale: float, causal: bool, s_total: int, world: int, rank: int, group=None,
+              partial_fn=None, combine_fn=None):
+    """Ring attention: queries, keys and values of a sequence of ``s_total`` positions are all sharded over the ranks
+    (rank r holds positions ``kv_shard_range(s_total, world, r)`` of Q [B,Hq,S_r,D] and of K / V [B,Hkv,S_r,D]).
+    In step t a rank runs the KV-shard pass of its queries over the shard of rank (r - t) mod world while that shard
+    travels on to rank r + 1 and the next one arrives from rank r - 1 (point-to-point, posted before the pass is
+    launched, awaited after it); the ``world`` partial results are merged by the state combine.  Returns
+    (O [B,Hq,S_r,D] bf16, LSE [B,Hq,S_r]) for the local queries.
+
+    Under the causal mask the passes over shards that lie in the future of the local queries are skipped (an empty
+    partial result stands in), so rank r does r + 1 passes: the work is not balanced across the ring (a zig-zag
+    assignment of positions to ranks would balance it; not done here).
+
+    ``partial_fn`` / ``combine_fn`` default to the CUDA entry points, as in ``attn_kv_sharded``."""
+    import torch
+    import torch.distributed as dist
+
+    if partial_fn is None or combine_fn is None:
+        from . import ops
+
+        partial_fn = partial_fn or ops.attn_fwd_bf16_kvshard
+        combine_fn = combine_fn or ops.attn_combine_partials
+    q0, q1 = kv_shard_range(s_total, world, rank)
+    if Q_local.shape[2] != q1 - q0 or K_local.shape[2] != q1 - q0 or V_local.shape != K_local.shape:
+        raise ValueError(f"rank {rank} must hold positions [{q0},{q1}) of {s_total}: Q {tuple(Q_local.shape)}, K {tuple(K_local.shape)}")
+    B, Hq, Sq, D = Q_local.shape
+    Hkv = K_local.shape[1]
+    rows = B * Hq * Sq
+    part_bytes = rows * (D * 4 + 8)
+    plan = ring_shard_plan(s_total, world, rank, causal)
+    parts = torch.empty((world, part_bytes), dtype=torch.uint8, device=Q_local.device)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    k_cur, v_cur = K_local, V_local
+    for t, (k_rank, (k0, k1), kv_pos0, total_arg, run) in enumerate(plan):
+        reqs, k_nxt, v_nxt = [], None, None
+        if t + 1 < world and world > 1:
+            n0, n1 = plan[t + 1][1]
+            k_nxt = torch.empty((B, Hkv, n1 - n0, D), dtype=K_local.dtype, device=K_local.device)
+            v_nxt = torch.empty_like(k_nxt)
+            ops_ = []
+            # bit patterns travel as bytes (every backend moves uint8); empty shards are not sent
+            if k_cur.numel() > 0:
+                ops_ += [dist.P2POp(dist.isend, k_cur.view(torch.uint8), nxt, group), dist.P2POp(dist.isend, v_cur.view(torch.uint8), nxt, group)]
+            if k_nxt.numel() > 0:
+                ops_ += [dist.P2POp(dist.irecv, k_nxt.view(torch.uint8), prv, group), dist.P2POp(dist.irecv, v_nxt.view(torch.uint8), prv, group)]
+            if ops_:
+                reqs = dist.batch_isend_irecv(ops_)
+        if run:
+            parts[t].copy_(partial_fn(Q_local, k_cur, v_cur, scale, causal, kv_pos0, total_arg))
+        elif rows > 0:
+            parts[t].copy_(empty_partial(rows, D, Q_local.device))
+        for r in reqs:
+            r.wait()
+        if k_nxt is not None:
+            k_cur, v_cur = k_nxt, v_nxt
+    if rows == 0:
+        return (torch.empty((B, Hq, 0, D), dtype=torch.bfloat16, device=Q_local.device),
+                torch.empty((B, Hq, 0), dtype=torch.float32, device=Q_local.device))
+    return combine_fn(parts, (B, Hq, Sq, D))
 
 
 def empty_partial(rows: int, D: int, device):

@@ -1,5 +1,6 @@
-"""Sequence-parallel attention on two real GPUs (skipped with fewer): one process per GPU, NCCL all-gather of the
-partial results, combine on every rank, against the CPU oracle.  NVLS is switched off for the child processes."""
+"""Sequence-parallel attention on two real GPUs (skipped with fewer): one process per GPU; KV-sharded attention (NCCL
+all-gather of the partial results, combine on every rank) and ring attention (K / V shards passed round by NCCL
+point-to-point sends), against the CPU oracle.  NVLS is switched off for the child processes."""
 import os
 import sys
 
@@ -40,6 +41,19 @@ def _worker(rank, world, port, q):
             u16 = lambda t: t.view(torch.uint16).numpy()
             Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
             out.append((float(np.abs(O.float().cpu().numpy() - oracle.bf16_decode(Ow)).max()), float(np.abs(L.cpu().numpy() - Lw).max())))
+        # ring attention: queries and keys sharded, K / V shards passed round by NCCL point-to-point sends
+        for (B, Hq, Hkv, S, causal) in ((1, 4, 2, 1024, True), (2, 4, 4, 640, True), (1, 2, 1, 512, False)):
+            Q, _, _, scale = pkg.synth.bf16_attention_inputs(B, Hq, S, 128, seed=23, Hkv=Hkv)
+            _, K, V, _ = pkg.synth.bf16_attention_inputs(B, Hkv, S, 128, seed=24)
+            p0, p1 = pkg.shard.kv_shard_range(S, world, rank)
+            O, L = pkg.shard.attn_ring(Q[:, :, p0:p1].contiguous().to(dev), K[:, :, p0:p1].contiguous().to(dev),
+                                       V[:, :, p0:p1].contiguous().to(dev), scale, causal, S, world, rank)
+            torch.cuda.synchronize()
+            pkg.ops.check_status(dev)
+            u16 = lambda t: t.view(torch.uint16).numpy()
+            Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
+            out.append((float(np.abs(O.float().cpu().numpy() - oracle.bf16_decode(Ow)[:, :, p0:p1]).max()),
+                        float(np.abs(L.cpu().numpy() - Lw[:, :, p0:p1]).max())))
         q.put((rank, out))
     finally:
         dist.destroy_process_group()

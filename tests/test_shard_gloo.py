@@ -177,3 +177,143 @@ def test_kv_sharded_attention_rank_without_keys_still_joins_the_exchange():
     assert [g[1] for g in got] == [(0, 128), (128, 256), (256, 256)]
     for _, _, err, lerr in got:
         assert err <= 1e-2 and lerr <= 1e-4
+
+
+def _cpu_stand_ins(oracle, B, Hq, Hkv, D):
+    """CPU stand-ins for the two CUDA entry points of sharded attention (partial result of a KV shard in the C-ABI byte
+    layout; state combine after the formula of the header)."""
+    import numpy as np
+    import torch
+
+    def u16(t):
+        return t.view(torch.uint16).numpy()
+
+    def partial_fn(Qt, Kt, Vt, scale, causal, kpos0, total):
+        Sq = Qt.shape[2]
+        q = oracle.bf16_decode(u16(Qt)).astype(np.float64)
+        k = oracle.bf16_decode(u16(Kt)).astype(np.float64)
+        v = oracle.bf16_decode(u16(Vt)).astype(np.float64)
+        grp = Hq // Hkv
+        o = np.zeros((B * Hq * Sq, D), np.float32)
+        ml = np.zeros((B * Hq * Sq, 2), np.float32)
+        for h in range(Hq):
+            s = q[0, h] @ k[0, h // grp].T * scale
+            if causal:
+                qi = np.arange(Sq)[:, None] + (total - Sq)
+                kj = np.arange(Kt.shape[2])[None, :] + kpos0
+                s = np.where(kj <= qi, s, -np.inf)
+            m = s.max(-1)
+            ok = np.isfinite(m)
+            p = np.where(ok[:, None], np.exp(s - np.where(ok, m, 0.0)[:, None]), 0.0)
+            o[h * Sq:(h + 1) * Sq] = p @ v[0, h // grp]
+            ml[h * Sq:(h + 1) * Sq, 0] = np.where(ok, m * 1.4426950408889634, -np.inf)
+            ml[h * Sq:(h + 1) * Sq, 1] = p.sum(-1)
+        return torch.from_numpy(np.concatenate([o.reshape(-1).view(np.uint8), ml.reshape(-1).view(np.uint8)]))
+
+    def combine_fn(gathered, shape):
+        rows = shape[0] * shape[1] * shape[2]
+        outs = np.zeros((rows, D)); den = np.zeros(rows); mm = np.full(rows, -np.inf)
+        shares = []
+        for z in range(gathered.shape[0]):
+            raw = gathered[z].numpy()
+            o = raw[: rows * D * 4].view(np.float32).reshape(rows, D).astype(np.float64)
+            ml = raw[rows * D * 4:].view(np.float32).reshape(rows, 2).astype(np.float64)
+            shares.append((o, ml))
+            mm = np.maximum(mm, np.where(ml[:, 1] > 0, ml[:, 0], -np.inf))
+        for o, ml in shares:
+            w = np.where(ml[:, 1] > 0, np.exp2(ml[:, 0] - mm), 0.0)
+            outs += w[:, None] * o
+            den += w * ml[:, 1]
+        return outs / den[:, None], (mm + np.log2(den)) * 0.6931471805599453
+
+    return u16, partial_fn, combine_fn
+
+
+def _ring_worker(rank, world, port, q, S, causal):
+    import importlib
+    import os
+    import sys
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        pkg = importlib.import_module("iro-cuda-ax_b200")
+        from oracle import host_oracle as oracle
+
+        B, Hq, Hkv, D = 1, 4, 2, 128
+        u16, partial_fn, combine_fn = _cpu_stand_ins(oracle, B, Hq, Hkv, D)
+        Q, _, _, scale = pkg.synth.bf16_attention_inputs(B, Hq, S, D, seed=5, Hkv=Hkv)
+        _, K, V, _ = pkg.synth.bf16_attention_inputs(B, Hkv, S, D, seed=6)
+        p0, p1 = pkg.shard.kv_shard_range(S, world, rank)
+        O, L = pkg.shard.attn_ring(Q[:, :, p0:p1].contiguous(), K[:, :, p0:p1].contiguous(), V[:, :, p0:p1].contiguous(), scale, causal, S,
+                                   world, rank, partial_fn=partial_fn, combine_fn=combine_fn)
+        err = lerr = 0.0
+        if p1 > p0:
+            Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
+            err = float(np.abs(np.asarray(O).reshape(B, Hq, p1 - p0, D) - oracle.bf16_decode(Ow)[:, :, p0:p1]).max())
+            lerr = float(np.abs(np.asarray(L).reshape(B, Hq, p1 - p0) - Lw[:, :, p0:p1]).max())
+        passes = sum(1 for step in pkg.shard.ring_shard_plan(S, world, rank, causal) if step[4])
+        q.put((rank, (p0, p1), err, lerr, passes))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run_ring(world, S, causal):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ring_worker, args=(r, world, port, q, S, causal)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        for p in procs:
+            p.join(180)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+    return sorted(q.get(timeout=5) for _ in range(world))
+
+
+def test_ring_attention_world_size_2_causal_and_full():
+    """Ring attention on two gloo ranks (queries and keys sharded, K / V shards passed round by point-to-point sends):
+    shard plan, causal position arguments, skipped future shards, exchange and combine, with CPU stand-ins for the two
+    CUDA entry points."""
+    got = _run_ring(2, 320, True)
+    assert [g[1] for g in got] == [(0, 256), (256, 320)]
+    assert [g[4] for g in got] == [1, 2]                  # under the causal mask rank r runs r + 1 passes
+    for _, _, err, lerr, _ in got:
+        assert err <= 1e-2 and lerr <= 1e-4
+    got = _run_ring(2, 320, False)
+    assert [g[4] for g in got] == [2, 2]
+    for _, _, err, lerr, _ in got:
+        assert err <= 1e-2 and lerr <= 1e-4
+
+
+def test_ring_attention_three_ranks_one_without_positions():
+    """Three ranks, two 128-position blocks: the last rank holds nothing, still forwards the shards it receives and
+    returns empty outputs."""
+    got = _run_ring(3, 256, True)
+    assert [g[1] for g in got] == [(0, 128), (128, 256), (256, 256)]
+    assert [g[4] for g in got] == [1, 2, 0]
+    for _, _, err, lerr, _ in got:
+        assert err <= 1e-2 and lerr <= 1e-4
+
+
+def test_ring_shard_plan_positions(pkg):
+    plan = pkg.shard.ring_shard_plan(640, 3, 1, True)         # rank 1 holds [256, 512)
+    assert [(s[0], s[1], s[4]) for s in plan] == [(1, (256, 512), True), (0, (0, 256), True), (2, (512, 640), False)]
+    assert all(s[3] == 512 for s in plan)                     # causal: the sequence as far as this rank's last query
+    assert [s[2] for s in plan] == [256, 0, 512]
+    assert all(s[3] == 640 and s[4] for s in pkg.shard.ring_shard_plan(640, 3, 1, False))

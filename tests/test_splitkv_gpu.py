@@ -204,6 +204,39 @@ def test_kv_sharded_partials_combine_to_full_attention(pkg, oracle, dev, B, Hq, 
     assert np.abs(L.cpu().numpy() - Lw).max() <= 1e-3
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,S,world,causal", [
+    (1, 4, 2, 1024, 2, True),
+    (1, 4, 2, 1024, 4, True),
+    (2, 4, 4, 640, 3, True),            # unequal shards: 256, 256, 128 positions
+    (1, 2, 1, 768, 3, False),
+    (1, 8, 2, 256, 4, True),            # more ranks than 128-position blocks: two ranks hold nothing
+])
+def test_ring_attention_plan_emulated_on_one_gpu(pkg, oracle, dev, B, Hq, Hkv, S, world, causal):
+    """Ring attention emulated on one GPU: for every virtual rank the KV-shard passes its plan prescribes (the real
+    CUDA entry point with the plan's position arguments; skipped passes as empty partial results), combined, against
+    the oracle's attention over the whole sequence, rows of that rank."""
+    Q, K, V, scale = make(pkg, B, Hq, Hkv, S, S, seed=17)
+    Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
+    Ow = oracle.bf16_decode(Ow)
+    for rank in range(world):
+        q0, q1 = pkg.shard.kv_shard_range(S, world, rank)
+        if q1 == q0:
+            continue
+        Ql = Q[:, :, q0:q1].contiguous().to(dev)
+        rows = B * Hq * (q1 - q0)
+        parts = []
+        for k_rank, (k0, k1), kv_pos0, total_arg, run in pkg.shard.ring_shard_plan(S, world, rank, causal):
+            if run:
+                Kl, Vl = K[:, :, k0:k1].contiguous().to(dev), V[:, :, k0:k1].contiguous().to(dev)
+                parts.append(pkg.ops.attn_fwd_bf16_kvshard(Ql, Kl, Vl, scale, causal, kv_pos0, total_arg))
+            else:
+                parts.append(pkg.shard.empty_partial(rows, 128, dev))
+        O, L = pkg.ops.attn_combine_partials(torch.stack(parts), tuple(Ql.shape))
+        pkg.ops.check_status(dev)
+        assert np.abs(O.float().cpu().numpy() - Ow[:, :, q0:q1]).max() <= 2e-2, (rank, world)
+        assert np.abs(L.cpu().numpy() - Lw[:, :, q0:q1]).max() <= 1e-3, (rank, world)
+
+
 def test_fused_operator_goldens_on_gpu(pkg, dev, golden):
     """The widened operators against the committed float64 fixtures (no oracle in the loop)."""
     g = golden["fused_small"]
