@@ -16,7 +16,7 @@ The default run also times, in the same process, the other workloads of the metr
 of at least two seconds ("sustained") and one library E4M3 GEMM as a reference point ("library_reference").
 
 Other workloads (--workload): gemm_fp8_strong, gemm_bf16_gate_up, gemm_bf16_down, gemm_bf16_swiglu, gemm_fp8_swiglu,
-attn_bf16, attn_fp8, quantize_fp8, rmsnorm_quantize_fp8, attn_decode_bf16, attn_decode_fp8; attn_ring (two or more GPUs:
+attn_bf16, attn_fp8, quantize_fp8, rmsnorm_quantize_fp8, attn_decode_bf16, attn_decode_fp8; attn_ring / attn_ring_zigzag (two or more GPUs:
 ring attention over one sequence sharded by position, device timing only).
 
 `--impl reference` times the CPU host oracle (the reference library has no
@@ -577,11 +577,44 @@ class AttnRing(Workload):
         self.out = self.pkg.shard.attn_ring(Q, K, V, self.scale, True, self.S, self.world, self.rank)
 
 
+class AttnRingZigzag(AttnRing):
+    """The same sequence with the zig-zag assignment of positions (rank r holds chunks r and 2N - 1 - r of 2N): every
+    rank runs about the same number of passes under the causal mask."""
+
+    def __init__(self, pkg, dev, rank, world, sets=2):
+        Workload.__init__(self, pkg, dev, rank, world)
+        self.S = self.S_PER_GPU * world
+        self.name = (f"ring attention, zig-zag positions: bf16 causal, B=1 Hq=32 Hkv=8 D=128, ONE sequence of {self.S} positions over "
+                     f"{world} GPUs (two chunks of 4096 per GPU), K/V shards passed round a ring")
+        self.sharding_note = AttnRing.sharding_note.replace("causal: rank r runs r + 1 of the N passes",
+                                                            "zig-zag chunks r and 2N - 1 - r per rank: the causal passes are balanced")
+        self.ranges = pkg.shard.zigzag_ranges(self.S, world, rank)
+        self.job_flops = 0.5 * 4.0 * self.B * self.Hq * float(self.S) * self.S * self.D
+        self.flops = self.job_flops / world
+        self.bytes_min = 0
+        passes = sum(1 for t in range(world)
+                     for st in pkg.shard.ring_passes(self.ranges, pkg.shard.zigzag_ranges(self.S, world, (rank - t) % world), True, self.S) if st[4])
+        self.launches_per_step = passes + 2
+        self.kv_bytes_per_step = 2 * self.B * self.Hkv * self.S_PER_GPU * self.D * 2 * (world - 1)
+        self.sets = []
+        for s in range(sets):
+            Qs, Ks, Vs = [], [], []
+            for c, (a, b) in enumerate(self.ranges):
+                Q, _, _, self.scale = pkg.synth.bf16_attention_inputs(self.B, self.Hq, b - a, self.D, seed=100 * s + 2 * rank + c, Hkv=self.Hkv, device=dev)
+                _, K, V, _ = pkg.synth.bf16_attention_inputs(self.B, self.Hkv, b - a, self.D, seed=100 * s + 2 * rank + c + 50, device=dev)
+                Qs.append(Q); Ks.append(K); Vs.append(V)
+            self.sets.append((Qs, Ks, Vs))
+
+    def step(self, i):
+        Qs, Ks, Vs = self.sets[i % len(self.sets)]
+        self.out = self.pkg.shard.attn_ring_zigzag(Qs, Ks, Vs, self.scale, True, self.S, self.world, self.rank)
+
+
 def make_workload(name, pkg, dev, rank, world):
-    if name == "attn_ring":
+    if name in ("attn_ring", "attn_ring_zigzag"):
         if world < 2:
-            raise SystemExit("attn_ring needs --gpus >= 2 (one process per GPU under torchrun)")
-        return AttnRing(pkg, dev, rank, world)
+            raise SystemExit(f"{name} needs --gpus >= 2 (one process per GPU under torchrun)")
+        return (AttnRing if name == "attn_ring" else AttnRingZigzag)(pkg, dev, rank, world)
     if name == "gemm_fp8":
         return GemmFp8(pkg, dev, rank, world)
     if name == "gemm_fp8_strong":
@@ -944,7 +977,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="gemm_fp8",
-                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8", "attn_ring"])
+                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8", "attn_ring", "attn_ring_zigzag"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")

@@ -119,20 +119,29 @@ def ring_shard_plan(s_total: int, world: int, rank: int, causal: bool):
     return plan
 
 
-def attn_ring(Q_local, K_local, V_local, scale: float, causal: bool, s_total: int, world: int, rank: int, group=None,
-              partial_fn=None, combine_fn=None):
-    """Ring attention: queries, keys and values of a sequence of ``s_total`` positions are all sharded over the ranks
-    (rank r holds positions ``kv_shard_range(s_total, world, r)`` of Q [B,Hq,S_r,D] and of K / V [B,Hkv,S_r,D]).
-    In step t a rank runs the KV-shard pass of its queries over the shard of rank (r - t) mod world while that shard
-    travels on to rank r + 1 and the next one arrives from rank r - 1 (point-to-point, posted before the pass is
-    launched, awaited after it); the ``world`` partial results are merged by the state combine.  Returns
-    (O [B,Hq,S_r,D] bf16, LSE [B,Hq,S_r]) for the local queries.
+def zigzag_ranges(s_total: int, world: int, rank: int) -> list[tuple[int, int]]:
+    """The two position ranges rank `rank` holds under the zig-zag assignment: the sequence is cut into 2 * world chunks
+    (boundaries at multiples of 128) and rank r takes chunks r and 2 * world - 1 - r, an early and a late one, so that
+    under the causal mask every rank sees about the same number of (query, key) pairs."""
+    return [shard_range(s_total, 128, 2 * world, rank), shard_range(s_total, 128, 2 * world, 2 * world - 1 - rank)]
 
-    Under the causal mask the passes over shards that lie in the future of the local queries are skipped (an empty
-    partial result stands in), so rank r does r + 1 passes: the work is not balanced across the ring (a zig-zag
-    assignment of positions to ranks would balance it; not done here).
 
-    ``partial_fn`` / ``combine_fn`` default to the CUDA entry points, as in ``attn_kv_sharded``."""
+def ring_passes(q_ranges, k_ranges, causal: bool, s_total: int):
+    """The KV-shard passes of one ring step: for every local query range and every key range of the shard in hand,
+    ``(qi, kj, kv_pos0, skv_total_arg, run)`` with the position arguments of ``axp_sm100_attn_fwd_bf16_kvshard`` (see
+    ``ring_shard_plan``).  Ranges are aligned and disjoint, so a key range lies wholly before a query range, is the
+    same range (the diagonal), or lies wholly after it - and is then skipped under the causal mask."""
+    out = []
+    for qi, (q0, q1) in enumerate(q_ranges):
+        for kj, (k0, k1) in enumerate(k_ranges):
+            run = k1 > k0 and q1 > q0 and not (causal and k0 >= q1)
+            out.append((qi, kj, k0, q1 if causal else s_total, run))
+    return out
+
+
+def _ring(Qs, Ks, Vs, ranges_of, scale, causal, s_total, world, rank, group, partial_fn, combine_fn):
+    """Ring attention over lists of position ranges per rank (one range: contiguous shards; two: zig-zag).  Qs / Ks / Vs are
+    lists of contiguous tensors, one per range of this rank."""
     import torch
     import torch.distributed as dist
 
@@ -141,43 +150,78 @@ def attn_ring(Q_local, K_local, V_local, scale: float, causal: bool, s_total: in
 
         partial_fn = partial_fn or ops.attn_fwd_bf16_kvshard
         combine_fn = combine_fn or ops.attn_combine_partials
-    q0, q1 = kv_shard_range(s_total, world, rank)
-    if Q_local.shape[2] != q1 - q0 or K_local.shape[2] != q1 - q0 or V_local.shape != K_local.shape:
-        raise ValueError(f"rank {rank} must hold positions [{q0},{q1}) of {s_total}: Q {tuple(Q_local.shape)}, K {tuple(K_local.shape)}")
-    B, Hq, Sq, D = Q_local.shape
-    Hkv = K_local.shape[1]
-    rows = B * Hq * Sq
-    part_bytes = rows * (D * 4 + 8)
-    plan = ring_shard_plan(s_total, world, rank, causal)
-    parts = torch.empty((world, part_bytes), dtype=torch.uint8, device=Q_local.device)
+    mine = ranges_of(rank)
+    for t_, (p0, p1) in zip(zip(Qs, Ks, Vs), mine):
+        if t_[0].shape[2] != p1 - p0 or t_[1].shape[2] != p1 - p0 or t_[2].shape != t_[1].shape:
+            raise ValueError(f"rank {rank} must hold positions [{p0},{p1}) of {s_total}: Q {tuple(t_[0].shape)}, K {tuple(t_[1].shape)}")
+    B, Hq, _, D = Qs[0].shape
+    Hkv = Ks[0].shape[1]
+    dev = Qs[0].device
     nxt, prv = (rank + 1) % world, (rank - 1) % world
-    k_cur, v_cur = K_local, V_local
-    for t, (k_rank, (k0, k1), kv_pos0, total_arg, run) in enumerate(plan):
+    parts = [[] for _ in mine]             # per local query range: the partial results of the passes that ran
+    k_cur, v_cur = list(Ks), list(Vs)
+    for t in range(world):
+        k_rank = (rank - t) % world
         reqs, k_nxt, v_nxt = [], None, None
-        if t + 1 < world and world > 1:
-            n0, n1 = plan[t + 1][1]
-            k_nxt = torch.empty((B, Hkv, n1 - n0, D), dtype=K_local.dtype, device=K_local.device)
-            v_nxt = torch.empty_like(k_nxt)
+        if t + 1 < world:
+            k_nxt = [torch.empty((B, Hkv, n1 - n0, D), dtype=Ks[0].dtype, device=dev) for n0, n1 in ranges_of((rank - t - 1) % world)]
+            v_nxt = [torch.empty_like(x) for x in k_nxt]
             ops_ = []
             # bit patterns travel as bytes (every backend moves uint8); empty shards are not sent
-            if k_cur.numel() > 0:
-                ops_ += [dist.P2POp(dist.isend, k_cur.view(torch.uint8), nxt, group), dist.P2POp(dist.isend, v_cur.view(torch.uint8), nxt, group)]
-            if k_nxt.numel() > 0:
-                ops_ += [dist.P2POp(dist.irecv, k_nxt.view(torch.uint8), prv, group), dist.P2POp(dist.irecv, v_nxt.view(torch.uint8), prv, group)]
+            for x in k_cur + v_cur:
+                if x.numel() > 0:
+                    ops_.append(dist.P2POp(dist.isend, x.view(torch.uint8), nxt, group))
+            for x in k_nxt + v_nxt:
+                if x.numel() > 0:
+                    ops_.append(dist.P2POp(dist.irecv, x.view(torch.uint8), prv, group))
             if ops_:
                 reqs = dist.batch_isend_irecv(ops_)
-        if run:
-            parts[t].copy_(partial_fn(Q_local, k_cur, v_cur, scale, causal, kv_pos0, total_arg))
-        elif rows > 0:
-            parts[t].copy_(empty_partial(rows, D, Q_local.device))
+        for qi, kj, kv_pos0, total_arg, run in ring_passes(mine, ranges_of(k_rank), causal, s_total):
+            if run:
+                parts[qi].append(partial_fn(Qs[qi], k_cur[kj], v_cur[kj], scale, causal, kv_pos0, total_arg))
         for r in reqs:
             r.wait()
         if k_nxt is not None:
             k_cur, v_cur = k_nxt, v_nxt
-    if rows == 0:
-        return (torch.empty((B, Hq, 0, D), dtype=torch.bfloat16, device=Q_local.device),
-                torch.empty((B, Hq, 0), dtype=torch.float32, device=Q_local.device))
-    return combine_fn(parts, (B, Hq, Sq, D))
+    outs = []
+    for qi, (p0, p1) in enumerate(mine):
+        if p1 == p0:
+            outs.append((torch.empty((B, Hq, 0, D), dtype=torch.bfloat16, device=dev), torch.empty((B, Hq, 0), dtype=torch.float32, device=dev)))
+            continue
+        if not parts[qi]:       # cannot happen with whole sequences (the diagonal pass always runs); kept for odd inputs
+            parts[qi].append(empty_partial(B * Hq * (p1 - p0), D, dev))
+        outs.append(combine_fn(torch.stack(parts[qi]), (B, Hq, p1 - p0, D)))
+    return outs
+
+
+def attn_ring(Q_local, K_local, V_local, scale: float, causal: bool, s_total: int, world: int, rank: int, group=None,
+              partial_fn=None, combine_fn=None):
+    """Ring attention: queries, keys and values of a sequence of ``s_total`` positions are all sharded over the ranks
+    (rank r holds positions ``kv_shard_range(s_total, world, r)`` of Q [B,Hq,S_r,D] and of K / V [B,Hkv,S_r,D]).
+    In step t a rank runs the KV-shard pass of its queries over the shard of rank (r - t) mod world while that shard
+    travels on to rank r + 1 and the next one arrives from rank r - 1 (point-to-point, posted before the pass is
+    launched, awaited after it); the partial results are merged by the state combine.  Returns
+    (O [B,Hq,S_r,D] bf16, LSE [B,Hq,S_r]) for the local queries.
+
+    Under the causal mask the passes over shards that lie in the future of the local queries are skipped, so rank r
+    does r + 1 passes: the work is not balanced across the ring; ``attn_ring_zigzag`` balances it.
+
+    ``partial_fn`` / ``combine_fn`` default to the CUDA entry points, as in ``attn_kv_sharded``."""
+    return _ring([Q_local], [K_local], [V_local], lambda r: [kv_shard_range(s_total, world, r)], scale, causal, s_total, world, rank,
+                 group, partial_fn, combine_fn)[0]
+
+
+def attn_ring_zigzag(Qs, Ks, Vs, scale: float, causal: bool, s_total: int, world: int, rank: int, group=None, partial_fn=None,
+                     combine_fn=None):
+    """Ring attention with the zig-zag assignment of positions: rank r holds the two ranges ``zigzag_ranges(s_total,
+    world, r)`` (an early and a late chunk of the sequence) as two contiguous tensors each of Q, K and V
+    (``Qs = (Q_early, Q_late)`` ...).  A ring step runs up to four KV-shard passes (each local query chunk against each
+    chunk of the shard in hand; under the causal mask the ones in the future are skipped), so every rank does about the
+    same work.  Returns ``[(O_early, LSE_early), (O_late, LSE_late)]``."""
+    if len(Qs) != 2 or len(Ks) != 2 or len(Vs) != 2:
+        raise ValueError("zig-zag ring attention takes the early and the late chunk: two tensors each of Q, K and V")
+    return _ring(list(Qs), list(Ks), list(Vs), lambda r: zigzag_ranges(s_total, world, r), scale, causal, s_total, world, rank, group,
+                 partial_fn, combine_fn)
 
 
 def empty_partial(rows: int, D: int, device):

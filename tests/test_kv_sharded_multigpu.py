@@ -54,6 +54,21 @@ def _worker(rank, world, port, q):
             Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
             out.append((float(np.abs(O.float().cpu().numpy() - oracle.bf16_decode(Ow)[:, :, p0:p1]).max()),
                         float(np.abs(L.cpu().numpy() - Lw[:, :, p0:p1]).max())))
+        # the zig-zag ring: two position ranges per rank
+        for (B, Hq, Hkv, S, causal) in ((1, 4, 2, 1024, True), (1, 2, 1, 640, False)):
+            Q, _, _, scale = pkg.synth.bf16_attention_inputs(B, Hq, S, 128, seed=25, Hkv=Hkv)
+            _, K, V, _ = pkg.synth.bf16_attention_inputs(B, Hkv, S, 128, seed=26)
+            ranges = pkg.shard.zigzag_ranges(S, world, rank)
+            cut = lambda T: [T[:, :, a:b].contiguous().to(dev) for a, b in ranges]
+            outs = pkg.shard.attn_ring_zigzag(cut(Q), cut(K), cut(V), scale, causal, S, world, rank)
+            torch.cuda.synchronize()
+            pkg.ops.check_status(dev)
+            u16 = lambda t: t.view(torch.uint16).numpy()
+            Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
+            for (p0, p1), (O, L) in zip(ranges, outs):
+                if p1 > p0:
+                    out.append((float(np.abs(O.float().cpu().numpy() - oracle.bf16_decode(Ow)[:, :, p0:p1]).max()),
+                                float(np.abs(L.cpu().numpy() - Lw[:, :, p0:p1]).max())))
         q.put((rank, out))
     finally:
         dist.destroy_process_group()

@@ -229,7 +229,7 @@ def _cpu_stand_ins(oracle, B, Hq, Hkv, D):
     return u16, partial_fn, combine_fn
 
 
-def _ring_worker(rank, world, port, q, S, causal):
+def _ring_worker(rank, world, port, q, S, causal, zigzag=False):
     import importlib
     import os
     import sys
@@ -249,27 +249,37 @@ def _ring_worker(rank, world, port, q, S, causal):
         u16, partial_fn, combine_fn = _cpu_stand_ins(oracle, B, Hq, Hkv, D)
         Q, _, _, scale = pkg.synth.bf16_attention_inputs(B, Hq, S, D, seed=5, Hkv=Hkv)
         _, K, V, _ = pkg.synth.bf16_attention_inputs(B, Hkv, S, D, seed=6)
-        p0, p1 = pkg.shard.kv_shard_range(S, world, rank)
-        O, L = pkg.shard.attn_ring(Q[:, :, p0:p1].contiguous(), K[:, :, p0:p1].contiguous(), V[:, :, p0:p1].contiguous(), scale, causal, S,
-                                   world, rank, partial_fn=partial_fn, combine_fn=combine_fn)
+        Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
+        Ow = oracle.bf16_decode(Ow)
+        if zigzag:
+            ranges = pkg.shard.zigzag_ranges(S, world, rank)
+            cut = lambda T: [T[:, :, a:b].contiguous() for a, b in ranges]
+            outs = pkg.shard.attn_ring_zigzag(cut(Q), cut(K), cut(V), scale, causal, S, world, rank, partial_fn=partial_fn, combine_fn=combine_fn)
+            passes = sum(1 for t in range(world) for step in pkg.shard.ring_passes(ranges, pkg.shard.zigzag_ranges(S, world, (rank - t) % world), causal, S)
+                         if step[4])
+        else:
+            ranges = [pkg.shard.kv_shard_range(S, world, rank)]
+            p0, p1 = ranges[0]
+            outs = [pkg.shard.attn_ring(Q[:, :, p0:p1].contiguous(), K[:, :, p0:p1].contiguous(), V[:, :, p0:p1].contiguous(), scale, causal, S,
+                                        world, rank, partial_fn=partial_fn, combine_fn=combine_fn)]
+            passes = sum(1 for step in pkg.shard.ring_shard_plan(S, world, rank, causal) if step[4])
         err = lerr = 0.0
-        if p1 > p0:
-            Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
-            err = float(np.abs(np.asarray(O).reshape(B, Hq, p1 - p0, D) - oracle.bf16_decode(Ow)[:, :, p0:p1]).max())
-            lerr = float(np.abs(np.asarray(L).reshape(B, Hq, p1 - p0) - Lw[:, :, p0:p1]).max())
-        passes = sum(1 for step in pkg.shard.ring_shard_plan(S, world, rank, causal) if step[4])
-        q.put((rank, (p0, p1), err, lerr, passes))
+        for (p0, p1), (O, L) in zip(ranges, outs):
+            if p1 > p0:
+                err = max(err, float(np.abs(np.asarray(O).reshape(B, Hq, p1 - p0, D) - Ow[:, :, p0:p1]).max()))
+                lerr = max(lerr, float(np.abs(np.asarray(L).reshape(B, Hq, p1 - p0) - Lw[:, :, p0:p1]).max()))
+        q.put((rank, ranges[0] if not zigzag else tuple(ranges), err, lerr, passes))
     finally:
         dist.destroy_process_group()
 
 
-def _run_ring(world, S, causal):
+def _run_ring(world, S, causal, zigzag=False):
     import torch.multiprocessing as mp
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_ring_worker, args=(r, world, port, q, S, causal)) for r in range(world)]
+    procs = [ctx.Process(target=_ring_worker, args=(r, world, port, q, S, causal, zigzag)) for r in range(world)]
     for p in procs:
         p.start()
     try:
@@ -317,3 +327,17 @@ def test_ring_shard_plan_positions(pkg):
     assert all(s[3] == 512 for s in plan)                     # causal: the sequence as far as this rank's last query
     assert [s[2] for s in plan] == [256, 0, 512]
     assert all(s[3] == 640 and s[4] for s in pkg.shard.ring_shard_plan(640, 3, 1, False))
+
+
+def test_zigzag_ring_attention_balances_the_causal_passes():
+    """Zig-zag assignment on two gloo ranks: four chunks, rank r holds chunks r and 3 - r; results equal attention over the
+    whole sequence on both chunks of every rank, and under the causal mask both ranks run the same number of passes."""
+    got = _run_ring(2, 1024, True, zigzag=True)
+    assert [g[1] for g in got] == [((0, 256), (768, 1024)), ((256, 512), (512, 768))]
+    assert [g[4] for g in got] == [5, 5]                  # of the 4 x 4 chunk pairs the causal mask keeps 10
+    for _, _, err, lerr, _ in got:
+        assert err <= 1e-2 and lerr <= 1e-4
+    got = _run_ring(2, 640, False, zigzag=True)               # unequal chunks: 256, 128, 128, 128 positions
+    assert [g[1] for g in got] == [((0, 256), (512, 640)), ((256, 384), (384, 512))]
+    for _, _, err, lerr, _ in got:
+        assert err <= 1e-2 and lerr <= 1e-4

@@ -237,6 +237,41 @@ def test_ring_attention_plan_emulated_on_one_gpu(pkg, oracle, dev, B, Hq, Hkv, S
         assert np.abs(L.cpu().numpy() - Lw[:, :, q0:q1]).max() <= 1e-3, (rank, world)
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,S,world,causal", [
+    (1, 4, 2, 1024, 2, True),
+    (1, 4, 2, 2048, 4, True),
+    (1, 2, 1, 640, 2, False),           # unequal chunks
+    (1, 4, 4, 384, 2, True),            # three 128-position blocks over four chunks: one chunk is empty
+])
+def test_zigzag_ring_passes_emulated_on_one_gpu(pkg, oracle, dev, B, Hq, Hkv, S, world, causal):
+    """Zig-zag ring attention emulated on one GPU: for every virtual rank and each of its two position ranges, the passes
+    ``ring_passes`` prescribes over all ranks' ranges (real CUDA entry point), combined, against the oracle."""
+    Q, K, V, scale = make(pkg, B, Hq, Hkv, S, S, seed=19)
+    Ow, Lw = oracle.attn_fwd_bf16_qkv(u16(Q), u16(K), u16(V), scale, causal)
+    Ow = oracle.bf16_decode(Ow)
+    counts = []
+    for rank in range(world):
+        mine = pkg.shard.zigzag_ranges(S, world, rank)
+        parts = [[] for _ in mine]
+        for t in range(world):
+            theirs = pkg.shard.zigzag_ranges(S, world, (rank - t) % world)
+            for qi, kj, kv_pos0, total_arg, run in pkg.shard.ring_passes(mine, theirs, causal, S):
+                if run:
+                    (q0, q1), (k0, k1) = mine[qi], theirs[kj]
+                    parts[qi].append(pkg.ops.attn_fwd_bf16_kvshard(Q[:, :, q0:q1].contiguous().to(dev), K[:, :, k0:k1].contiguous().to(dev),
+                                                                   V[:, :, k0:k1].contiguous().to(dev), scale, causal, kv_pos0, total_arg))
+        counts.append(sum(len(p_) for p_ in parts))
+        for (q0, q1), ps in zip(mine, parts):
+            if q1 == q0:
+                continue
+            O, L = pkg.ops.attn_combine_partials(torch.stack(ps), (B, Hq, q1 - q0, 128))
+            pkg.ops.check_status(dev)
+            assert np.abs(O.float().cpu().numpy() - Ow[:, :, q0:q1]).max() <= 2e-2, (rank, q0)
+            assert np.abs(L.cpu().numpy() - Lw[:, :, q0:q1]).max() <= 1e-3, (rank, q0)
+    if causal and S % (256 * world) == 0:
+        assert len(set(counts)) == 1         # equal chunks: every rank runs the same number of passes
+
+
 def test_fused_operator_goldens_on_gpu(pkg, dev, golden):
     """The widened operators against the committed float64 fixtures (no oracle in the loop)."""
     g = golden["fused_small"]
