@@ -219,6 +219,13 @@ int axp_sm100_attn_fwd_bf16_kvshard(const void* Q, const void* K, const void* V,
                                     int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Skv_local, int64_t kv_pos0, int64_t Skv_total,
                                     int64_t D, float scale, int causal, int64_t bh_begin, int64_t bh_end, void* stream,
                                     uint32_t* status_dev);
+/* The same pass on E4M3 operands (Q, K, V bytes and per-head descales as for axp_sm100_attn_fwd_fp8): the partial result has
+ * the same layout and merges with axp_sm100_attn_combine_partials.  As in axp_sm100_attn_fwd_fp8_splitkv, every shard
+ * rounds its softmax weights to E4M3 against its own running maximum. */
+int axp_sm100_attn_fwd_fp8_kvshard(const void* Q, const void* K, const void* V, const float* q_descale, const float* k_descale,
+                                   const float* v_descale, void* partial, int64_t partial_bytes, int64_t B, int64_t Hq, int64_t Hkv,
+                                   int64_t Sq, int64_t Skv_local, int64_t kv_pos0, int64_t Skv_total, int64_t D, float scale,
+                                   int causal, int64_t bh_begin, int64_t bh_end, void* stream, uint32_t* status_dev);
 int axp_sm100_attn_combine_partials(const void* partials, int64_t num_shares, int64_t share_stride_bytes, void* O, float* LSE,
                                     int64_t rows, void* stream);
 

@@ -42,6 +42,7 @@ EXPORTS = (
     "axp_sm100_attn_fwd_fp8_splitkv",
     "axp_sm100_attn_partial_bytes",
     "axp_sm100_attn_fwd_bf16_kvshard",
+    "axp_sm100_attn_fwd_fp8_kvshard",
     "axp_sm100_attn_combine_partials",
     "axp_sm100_attn_splitkv_static_scratch_bytes",
     "axp_sm100_attn_fwd_bf16_splitkv_static",
@@ -144,6 +145,9 @@ def lib() -> ctypes.CDLL:
         L.axp_sm100_attn_fwd_bf16_kvshard.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64, ctypes.c_float,
                                                       ctypes.c_int, i64, i64, vp, u32p]
         L.axp_sm100_attn_fwd_bf16_kvshard.restype = ctypes.c_int
+        L.axp_sm100_attn_fwd_fp8_kvshard.argtypes = [vp, vp, vp, fp, fp, fp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64,
+                                                     ctypes.c_float, ctypes.c_int, i64, i64, vp, u32p]
+        L.axp_sm100_attn_fwd_fp8_kvshard.restype = ctypes.c_int
         L.axp_sm100_attn_combine_partials.argtypes = [vp, i64, i64, vp, fp, i64, vp]
         L.axp_sm100_attn_combine_partials.restype = ctypes.c_int
         L.axp_sm100_attn_splitkv_static_scratch_bytes.argtypes = []

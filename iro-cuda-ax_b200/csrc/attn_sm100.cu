@@ -1644,6 +1644,18 @@ extern "C" int axp_sm100_attn_fwd_bf16_kvshard(const void* Q, const void* K, con
                               partial_bytes, bh_begin, bh_end, stream, status_dev, /*stack_gqa=*/true, /*kv_shard=*/true, kv_pos0, Skv_total);
 }
 
+extern "C" int axp_sm100_attn_fwd_fp8_kvshard(const void* Q, const void* K, const void* V, const float* q_descale, const float* k_descale,
+                                              const float* v_descale, void* partial, int64_t partial_bytes, int64_t B, int64_t Hq,
+                                              int64_t Hkv, int64_t Sq, int64_t Skv_local, int64_t kv_pos0, int64_t Skv_total, int64_t D,
+                                              float scale, int causal, int64_t bh_begin, int64_t bh_end, void* stream,
+                                              uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_attn_fwd_fp8_kvshard");
+    if (!partial) return axp_shim::fail(AXP_ERR_BAD_ARG, "attn kvshard: partial buffer is null");
+    return launch_attn<true>(Q, K, V, q_descale, k_descale, v_descale, partial, nullptr, B, Hq, Hkv, Sq, Skv_local, D, scale, causal, 1,
+                             partial, partial_bytes, bh_begin, bh_end, stream, status_dev, /*stack_gqa=*/true, /*kv_shard=*/true, kv_pos0,
+                             Skv_total);
+}
+
 extern "C" int axp_sm100_attn_combine_partials(const void* partials, int64_t num_shares, int64_t share_stride_bytes, void* O, float* LSE,
                                                int64_t rows, void* stream) {
     axp_shim::NvtxRange nvtx_range("axp_sm100_attn_combine_partials");

@@ -337,6 +337,31 @@ def attn_fwd_bf16_kvshard(Q, K, V, scale: float, causal: bool, kv_pos0: int, skv
     return partial
 
 
+def attn_fwd_fp8_kvshard(Q, K, V, q_descale, k_descale, v_descale, scale: float, causal: bool, kv_pos0: int, skv_total: int,
+                         partial=None):
+    """``attn_fwd_bf16_kvshard`` on E4M3 operands (float8_e4m3fn or uint8 bytes) with per-head descales float32 [B*Hq] /
+    [B*Hkv]: the partial result of the local keys, for ``attn_combine_partials``."""
+    _need_cuda(Q, K, V, q_descale, k_descale, v_descale, partial)
+    if not (_is_fp8(Q) and _is_fp8(K) and _is_fp8(V)):
+        raise TypeError("Q, K, V must be float8_e4m3fn (or uint8 bytes)")
+    if Q.dim() != 4 or K.dim() != 4 or K.shape != V.shape or Q.shape[0] != K.shape[0] or Q.shape[3] != K.shape[3]:
+        raise ValueError("Q [B,Hq,Sq,D], K / V [B,Hkv,Skv_local,D]")
+    if not (Q.is_contiguous() and K.is_contiguous() and V.is_contiguous()):
+        raise ValueError("Q, K, V must be contiguous")
+    B, Hq, Sq, D = Q.shape
+    Hkv, Skv = K.shape[1], K.shape[2]
+    for d, n in ((q_descale, B * Hq), (k_descale, B * Hkv), (v_descale, B * Hkv)):
+        if d.dtype != torch.float32 or d.numel() != n or not d.is_contiguous():
+            raise ValueError("descales must be contiguous float32 of B*Hq / B*Hkv elements")
+    need = attn_partial_bytes(B * Hq, Sq)
+    if partial is None:
+        partial = torch.empty(need, dtype=torch.uint8, device=Q.device)
+    capi.check(capi.lib().axp_sm100_attn_fwd_fp8_kvshard(
+        _ptr(Q), _ptr(K), _ptr(V), _ptr(q_descale), _ptr(k_descale), _ptr(v_descale), _ptr(partial), partial.numel(), B, Hq, Hkv, Sq, Skv,
+        kv_pos0, skv_total, D, ctypes.c_float(scale), int(causal), 0, B * Hq, _stream(), _ptr(status_word(Q.device))))
+    return partial
+
+
 def attn_combine_partials(partials, shape, out=None, lse=None):
     """Merges partial results (``partials``: uint8 [shares, bytes], one row per share) into O ``shape`` = [B,Hq,Sq,D]
     bf16 and LSE [B,Hq,Sq]."""

@@ -119,6 +119,17 @@ def ring_shard_plan(s_total: int, world: int, rank: int, causal: bool):
     return plan
 
 
+def fp8_partial_fn(q_descale, k_descale, v_descale):
+    """``partial_fn`` for ``attn_kv_sharded`` / ``attn_ring`` / ``attn_ring_zigzag`` on E4M3 operands: the KV-shard pass of
+    ``axp_sm100_attn_fwd_fp8_kvshard`` with the per-head descales (float32 [B*Hq] / [B*Hkv]) bound."""
+    from . import ops
+
+    def partial_fn(Q, K, V, scale, causal, kv_pos0, skv_total):
+        return ops.attn_fwd_fp8_kvshard(Q, K, V, q_descale, k_descale, v_descale, scale, causal, kv_pos0, skv_total)
+
+    return partial_fn
+
+
 def zigzag_ranges(s_total: int, world: int, rank: int) -> list[tuple[int, int]]:
     """The two position ranges rank `rank` holds under the zig-zag assignment: the sequence is cut into 2 * world chunks
     (boundaries at multiples of 128) and rank r takes chunks r and 2 * world - 1 - r, an early and a late one, so that

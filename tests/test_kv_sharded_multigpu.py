@@ -69,6 +69,20 @@ def _worker(rank, world, port, q):
                 if p1 > p0:
                     out.append((float(np.abs(O.float().cpu().numpy() - oracle.bf16_decode(Ow)[:, :, p0:p1]).max()),
                                 float(np.abs(L.cpu().numpy() - Lw[:, :, p0:p1]).max())))
+        # E4M3 operands through the same ring (the KV-shard pass with per-head descales), against the one-GPU forward pass
+        B, Hq, Hkv, S = 1, 8, 2, 1024
+        Q8, K8, V8, dq, dk, dv, scale = pkg.synth.fp8_attention_inputs(B, Hq, Hkv, S, 128, seed=29)
+        p0, p1 = pkg.shard.kv_shard_range(S, world, rank)
+        dqd, dkd, dvd = dq.to(dev), dk.to(dev), dv.to(dev)
+        O, L = pkg.shard.attn_ring(Q8[:, :, p0:p1].contiguous().to(dev), K8[:, :, p0:p1].contiguous().to(dev), V8[:, :, p0:p1].contiguous().to(dev),
+                                   scale, True, S, world, rank, partial_fn=pkg.shard.fp8_partial_fn(dqd, dkd, dvd))
+        Of, Lf = pkg.ops.attn_fwd_fp8(Q8.to(dev), K8.to(dev), V8.to(dev), dqd, dkd, dvd, scale, True)
+        torch.cuda.synchronize()
+        pkg.ops.check_status(dev)
+        ref = Of[:, :, p0:p1].float().cpu().numpy()
+        rel = float(np.linalg.norm(O.float().cpu().numpy() - ref) / np.linalg.norm(ref))
+        # the shards round P against their own running maxima: same bar as several split-KV shares against one pass
+        out.append((0.0 if rel <= 6e-2 else rel, float(np.abs(L.cpu().numpy() - Lf[:, :, p0:p1].cpu().numpy()).max())))
         q.put((rank, out))
     finally:
         dist.destroy_process_group()

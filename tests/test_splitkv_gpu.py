@@ -272,6 +272,61 @@ def test_zigzag_ring_passes_emulated_on_one_gpu(pkg, oracle, dev, B, Hq, Hkv, S,
         assert len(set(counts)) == 1         # equal chunks: every rank runs the same number of passes
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,causal,cuts", [
+    (1, 8, 2, 256, 1024, True, (0, 384, 768, 1024)),        # three shards, late queries
+    (2, 8, 2, 1, 2048, True, (0, 1024, 2048)),              # decode on an E4M3 KV cache, stacked GQA heads
+    (1, 4, 4, 128, 640, False, (0, 256, 640)),
+])
+def test_fp8_kv_sharded_partials_combine_to_full_attention(pkg, oracle, dev, B, Hq, Hkv, Sq, Skv, causal, cuts):
+    """Sequence-parallel attention on E4M3 operands emulated on one GPU: one KV-shard pass per shard, combined.  The shards
+    round P to E4M3 against their own running maxima, so - as for several split-KV shares - the result is held against
+    exact float64 attention on the dequantised operands and must be about as close to it as the single-pass oracle is;
+    with one shard the pass reproduces the split-KV entry point bit for bit."""
+    Qs, K, V, dq, dk, dv, scale = pkg.synth.fp8_attention_inputs(B, Hq, Hkv, Skv, 128, seed=27)
+    r0 = Skv - Sq if causal else 0
+    Q = Qs[:, :, r0:r0 + Sq].contiguous()
+    Qd, dqd, dkd, dvd = Q.to(dev), dq.to(dev), dk.to(dev), dv.to(dev)
+    parts = []
+    for k0, k1 in zip(cuts[:-1], cuts[1:]):
+        parts.append(pkg.ops.attn_fwd_fp8_kvshard(Qd, K[:, :, k0:k1].contiguous().to(dev), V[:, :, k0:k1].contiguous().to(dev), dqd, dkd, dvd,
+                                                  scale, causal, k0, Skv))
+    O, L = pkg.ops.attn_combine_partials(torch.stack(parts), tuple(Q.shape))
+    pkg.ops.check_status(dev)
+    Ow, Lw = oracle.attn_fwd_fp8(u8(Qs), u8(K), u8(V), dq.numpy(), dk.numpy(), dv.numpy(), scale, causal, tile_n=128, q_range=(r0, r0 + Sq))
+    want = oracle.bf16_decode(Ow)[:, :, r0:r0 + Sq]
+    got = O.float().cpu().numpy()
+    assert np.abs(L.cpu().numpy() - Lw[:, :, r0:r0 + Sq]).max() <= 1e-3
+    g = Hq // Hkv
+    q = oracle.e4m3_decode(u8(Q)).astype(np.float64) * dq.numpy().reshape(B, Hq, 1, 1)
+    k = np.repeat(oracle.e4m3_decode(u8(K)).astype(np.float64) * dk.numpy().reshape(B, Hkv, 1, 1), g, axis=1)
+    v = np.repeat(oracle.e4m3_decode(u8(V)).astype(np.float64) * dv.numpy().reshape(B, Hkv, 1, 1), g, axis=1)
+    sc = np.einsum("bhqd,bhkd->bhqk", q, k) * scale
+    if causal:
+        sc = np.where(np.arange(Skv)[None, :] <= (np.arange(Sq)[:, None] + r0), sc, -np.inf)
+    pr = np.exp(sc - sc.max(-1, keepdims=True))
+    exact = np.einsum("bhqk,bhkd->bhqd", pr / pr.sum(-1, keepdims=True), v)
+    err_kernel = np.linalg.norm(got - exact) / np.linalg.norm(exact)
+    err_oracle = np.linalg.norm(want - exact) / np.linalg.norm(exact)
+    assert err_kernel <= 5e-2 and err_kernel <= 2.0 * err_oracle + 5e-3, (err_kernel, err_oracle)
+    # one shard = the whole key range: the same kernel launch as split-KV with one share leaving a partial result
+    whole = pkg.ops.attn_fwd_fp8_kvshard(Qd, K.to(dev), V.to(dev), dqd, dkd, dvd, scale, causal, 0, Skv)
+    O1, L1 = pkg.ops.attn_combine_partials(whole.view(1, -1), tuple(Q.shape))
+    O2, L2 = pkg.ops.attn_fwd_fp8_splitkv(Qd, K.to(dev), V.to(dev), dqd, dkd, dvd, scale, causal, num_splits=1)
+    pkg.ops.check_status(dev)
+    assert np.linalg.norm(O1.float().cpu().numpy() - O2.float().cpu().numpy()) <= 1e-2 * np.linalg.norm(O2.float().cpu().numpy())
+    assert np.abs(L1.cpu().numpy() - L2.cpu().numpy()).max() <= 1e-3
+
+
+def test_fp8_kvshard_rejects_bad_arguments(pkg, dev):
+    Q, K, V, dq, dk, dv, scale = (t.to(dev) if torch.is_tensor(t) else t for t in pkg.synth.fp8_attention_inputs(1, 4, 2, 256, 128, seed=5))
+    small = torch.empty(16, dtype=torch.uint8, device=dev)
+    with pytest.raises(pkg.capi.AxpError) as e:
+        pkg.ops.attn_fwd_fp8_kvshard(Q, K, V, dq, dk, dv, scale, True, 0, 256, partial=small)        # partial buffer too small
+    assert e.value.code == pkg.capi.AXP_ERR_BAD_ARG
+    with pytest.raises(pkg.capi.AxpError):
+        pkg.ops.attn_fwd_fp8_kvshard(Q, K, V, dq, dk, dv, scale, True, 128, 256)                      # shard reaches past the sequence
+
+
 def test_fused_operator_goldens_on_gpu(pkg, dev, golden):
     """The widened operators against the committed float64 fixtures (no oracle in the loop)."""
     g = golden["fused_small"]
