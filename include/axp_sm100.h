@@ -258,7 +258,8 @@ int axp_sm100_selftest_bounded_wait(int64_t limit_cycles, void* stream, uint32_t
 /* Process-wide tuning option; value 0 restores the library default.
  *   "gemm.epilogue_warpgroups"  2 or 4: warpgroups that drain the accumulator
  *   "gemm.cta_group"            1 or 2: CTAs cooperating on one MMA (2 = cluster pair, the default for both GEMMs:
- *                               256 x 256 tile per pair, each CTA loads its own operand halves)
+ *                               256 x 256 tile per pair, each CTA loads its own operand halves; the E4M3 gate / up
+ *                               (SwiGLU) GEMM runs single CTAs unless 2 is chosen)
  *   "gemm.fp8_tile"             FP8 block-scaled GEMM: 256 = 128 x 256 tiles per CTA (default); 128 = 128 x 128
  *                               tiles with two CTAs per SM (same results bit for bit; measured 13 % slower on 8192^3)
  *   "attn.exp_mode"             how the softmax exponentials are evaluated: 1 = all on the SFU;

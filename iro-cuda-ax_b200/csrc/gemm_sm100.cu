@@ -153,8 +153,8 @@ template <bool kFp8, int kEpiWG, int kCtaGroup, bool kGated = false>
 __global__ void __launch_bounds__(128 * (1 + kEpiWG), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
-    static_assert(!kGated || (!kFp8 && kEpiWG == 4) || (kFp8 && kEpiWG == 2 && kCtaGroup == 1),
-                  "the gated epilogue exists for bf16 with four epilogue warpgroups and for FP8 with two, one CTA per MMA");
+    static_assert(!kGated || (!kFp8 && kEpiWG == 4) || (kFp8 && kEpiWG == 2),
+                  "the gated epilogue exists for bf16 with four epilogue warpgroups and for FP8 with two");
     constexpr int kOutN = kGated ? kBN / 2 : kBN;     // output columns per tile
     using SC = StageCfg<kCtaGroup>;
     constexpr int kStages = SC::kStages;
@@ -1006,29 +1006,38 @@ int launch_gated_fp8(const void* X, const void* Wg, const void* Wu, const float*
     p.alpha = 1.0f;
     p.ldc = ldh;
     p.status = status_dev;
-    const int64_t tiles = ((M + kBM - 1) / kBM) * ((n_local + kBN / 2 - 1) / (kBN / 2));
-    const int grid = int(tiles < dev.sm_count ? tiles : dev.sm_count);
-    auto kernel = gemm_kernel<true, 2, 1, true>;
-    static thread_local int attr_set_for_device = -1;
-    if (attr_set_for_device != dev.device) {
-        if (int rc = check_register_pool(kernel, 384, 128 * 40 + 256 * 232, "gemm fp8 swiglu"); rc != AXP_OK) return rc;
-        AXP_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, StageCfg<1>::kDynSmem));
-        attr_set_for_device = dev.device;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(grid), 1, 1);
-    cfg.blockDim = dim3(384, 1, 1);
-    cfg.dynamicSmemBytes = size_t(StageCfg<1>::kDynSmem);
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    AXP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmA, tmG, tmU, p));
-    return AXP_OK;
+    // Single CTAs by default: with two scale streams per K block the pair form (the leader stages the gate rows, its peer
+    // the up rows; option "gemm.cta_group" = 2) measured slower here (1681 against 1826 TFLOP/s on the MLP gate / up shape),
+    // unlike the plain block-scaled kernel.
+    const int cta_group = option_slot(kOptGemmCtaGroup).load(std::memory_order_relaxed) == 2 ? 2 : 1;
+    const int64_t tile_m = kBM * cta_group;
+    const int64_t tiles = ((M + tile_m - 1) / tile_m) * ((n_local + kBN / 2 - 1) / (kBN / 2));
+    const int64_t slots = dev.sm_count / cta_group;
+    const int grid = int(tiles < slots ? tiles : slots) * cta_group;
+    static thread_local int attr_set_for_device[2] = {-1, -1};
+    auto launch = [&](auto kernel, int smem_bytes, int slot) -> int {
+        if (attr_set_for_device[slot] != dev.device) {
+            if (int rc = check_register_pool(kernel, 384, 128 * 40 + 256 * 232, "gemm fp8 swiglu"); rc != AXP_OK) return rc;
+            AXP_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+            attr_set_for_device[slot] = dev.device;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(grid), 1, 1);
+        cfg.blockDim = dim3(384, 1, 1);
+        cfg.dynamicSmemBytes = size_t(smem_bytes);
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = unsigned(cta_group);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        AXP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmA, tmG, tmU, p));
+        return AXP_OK;
+    };
+    if (cta_group == 2) return launch(gemm_kernel<true, 2, 2, true>, StageCfg<2>::kDynSmem, 1);
+    return launch(gemm_kernel<true, 2, 1, true>, StageCfg<1>::kDynSmem, 0);
 }
 
 }  // namespace
