@@ -311,6 +311,25 @@ def test_fp8_swiglu_gate_up_projection(pkg, oracle, dev):
             assert torch.isnan(H[:, :n0]).all() and torch.isnan(H[:, n1:]).all()
 
 
+def test_fp8_swiglu_cta_pair_option_reproduces_the_default(pkg, dev):
+    """The CTA-pair form of the E4M3 gate / up pass (option gemm.cta_group = 2; single CTAs are the default) gives the same
+    bits, on full tiles, a ragged shape and a column shard."""
+    for (M, N, K, n_range) in ((512, 512, 512, None), (200, 392, 256, None), (384, 1024, 384, (128, 648))):
+        X, Wg, sX, sWg = pkg.synth.fp8_gemm_inputs(M, N, K, seed=71)
+        _, Wu, _, sWu = pkg.synth.fp8_gemm_inputs(M, N, K, seed=72)
+        d = [t.to(dev) for t in (X, Wg, Wu, sX * 0.0625, sWg, sWu)]
+        H1 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+        pkg.ops.gemm_fp8_blockscaled_swiglu(*d, out=H1, n_range=n_range)
+        pkg.capi.set_option("gemm.cta_group", 2)
+        try:
+            H2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+            pkg.ops.gemm_fp8_blockscaled_swiglu(*d, out=H2, n_range=n_range)
+        finally:
+            pkg.capi.set_option("gemm.cta_group", 0)
+        pkg.ops.check_status(dev)
+        assert torch.equal(H1.view(torch.int16), H2.view(torch.int16))
+
+
 def test_fp8_swiglu_equals_two_gemms_and_elementwise(pkg, oracle, dev):
     """Property at MLP size: the fused pass agrees with SiLU(G) * U from two plain block-scaled GEMM launches (which
     round G and U to bf16 first, hence the tolerance); sampled rows agree with the oracle; a column-sharded run
