@@ -211,7 +211,8 @@ def attn_ring(Q_local, K_local, V_local, scale: float, causal: bool, s_total: in
     (rank r holds positions ``kv_shard_range(s_total, world, r)`` of Q [B,Hq,S_r,D] and of K / V [B,Hkv,S_r,D]).
     In step t a rank runs the KV-shard pass of its queries over the shard of rank (r - t) mod world while that shard
     travels on to rank r + 1 and the next one arrives from rank r - 1 (point-to-point, posted before the pass is
-    launched, awaited after it); the partial results are merged by the state combine.  Returns
+    launched, awaited after it); the partial results are merged by the state combine (the reference's
+    CombineSoftmaxStateF32, include/axp/level3/recipes/attention/process.hpp:107-164, across ranks).  Returns
     (O [B,Hq,S_r,D] bf16, LSE [B,Hq,S_r]) for the local queries.
 
     Under the causal mask the passes over shards that lie in the future of the local queries are skipped, so rank r
