@@ -16,6 +16,7 @@ The default run also times, in the same process, the other workloads of the metr
 of at least two seconds ("sustained") and one library E4M3 GEMM as a reference point ("library_reference").
 
 Other workloads (--workload): gemm_fp8_strong, gemm_bf16_gate_up, gemm_bf16_down, gemm_bf16_swiglu, gemm_fp8_swiglu,
+gemm_fp8_swiglu_quant (quantising epilogue) / gemm_fp8_swiglu_then_quant (the same result from two kernels),
 attn_bf16, attn_fp8, quantize_fp8, rmsnorm_quantize_fp8, attn_decode_bf16, attn_decode_fp8; attn_ring / attn_ring_zigzag (two or more GPUs:
 ring attention over one sequence sharded by position, device timing only).
 
@@ -287,6 +288,35 @@ class GemmFp8SwiGLU(Workload):
         x, wg, wu = X[:rows].view(torch.uint8).cpu().numpy(), Wg.view(torch.uint8).cpu().numpy(), Wu.view(torch.uint8).cpu().numpy()
         sx, sg, su = sX[:rows].cpu().numpy(), sWg.cpu().numpy(), sWu.cpu().numpy()
         return (lambda: oracle.gemm_fp8_blockscaled_swiglu(x, wg, wu, sx, sg, su)), 2.0 * rows * 2 * self.N * self.K
+
+
+class GemmFp8SwiGLUQuant(GemmFp8SwiGLU):
+    """The FP8 gate / up pass with the quantising epilogue: H leaves as E4M3 + 1x128 scales (the down projection's A operand),
+    `--two-kernels` semantics for comparison: the plain pass followed by the stand-alone quantiser (option below)."""
+
+    def __init__(self, pkg, dev, rank, world, fused=True, sets=2):
+        import torch
+
+        super().__init__(pkg, dev, rank, world, sets)
+        self.fused = fused
+        M, N = self.M, self.N
+        self.name = (f"cfg2 gate+up fused, FP8, E4M3 + 1x128 scales out ({'quantising epilogue' if fused else 'two kernels: bf16 H, then the quantiser'}), "
+                     f"M={M} N={N} K={self.K} per GPU (flops 2*M*2N*K)")
+        self.launches_per_step = 1 if fused else 2
+        self.q = [(torch.empty((M, N), dtype=torch.float8_e4m3fn, device=dev), torch.empty((M, N // 128), dtype=torch.float32, device=dev))
+                  for _ in range(sets)]
+
+    def step(self, i):
+        s, (Q, S) = self.sets[i % len(self.sets)], self.q[i % len(self.q)]
+        if self.fused:
+            self.pkg.ops.gemm_fp8_blockscaled_swiglu_quant(*s[:6], out=Q, scales=S)
+        else:
+            self.pkg.ops.gemm_fp8_blockscaled_swiglu(*s[:6], out=s[6])
+            self.pkg.ops.quantize_rows_e4m3(s[6], out=Q, scales=S)
+
+    def e2e_spec(self):
+        s, (Q, S) = self.sets[0], self.q[0]
+        return (lambda i, o: self.pkg.ops.gemm_fp8_blockscaled_swiglu_quant(*i, out=o[0], scales=o[1])), list(s[:6]), [Q, S]
 
 
 class AttnBf16(Workload):
@@ -627,6 +657,8 @@ def make_workload(name, pkg, dev, rank, world):
         return GemmBf16SwiGLU(pkg, dev, rank, world)
     if name == "gemm_fp8_swiglu":
         return GemmFp8SwiGLU(pkg, dev, rank, world)
+    if name in ("gemm_fp8_swiglu_quant", "gemm_fp8_swiglu_then_quant"):
+        return GemmFp8SwiGLUQuant(pkg, dev, rank, world, fused=(name == "gemm_fp8_swiglu_quant"))
     if name == "attn_decode_fp8":
         return AttnDecodeFp8(pkg, dev, rank, world)
     if name == "attn_bf16":
@@ -977,7 +1009,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="gemm_fp8",
-                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8", "attn_ring", "attn_ring_zigzag"])
+                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "gemm_fp8_swiglu_quant", "gemm_fp8_swiglu_then_quant", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8", "attn_ring", "attn_ring_zigzag"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")

@@ -138,6 +138,19 @@ int axp_sm100_gemm_fp8_blockscaled_swiglu(const void* X, const void* Wg, const v
                                           int64_t ldwu, int64_t ldh, int64_t n_begin, int64_t n_end, void* stream,
                                           uint32_t* status_dev);
 
+/* The same pass with a quantising epilogue: instead of bf16 H it leaves Hq [M,N] E4M3 bytes (leading dimension ldq
+ * bytes, a multiple of 16) and Hq_scales [M, N/128] fp32 - the A operand and the 1x128 scales of the next block-scaled
+ * GEMM (the MLP's down projection) - bit for bit what axp_sm100_quantize_rows_e4m3 produces from the bf16 H of the
+ * entry point above: the value is rounded to bf16 in registers, the block maximum of a row's 128 output columns is
+ * formed by the row's two epilogue threads, scale = max / 448, q = e4m3_sat(h * (1 / scale)).  H itself never reaches
+ * HBM.  Requires N % 128 == 0 and a column range of whole 128-column blocks; rank-sharded calls write their blocks of
+ * Hq_scales.  Realizes: the gated epilogue above followed by the reference's CastTile with the fp8_saturate policy
+ * (include/axp/protocol/convert/contracts.hpp:31, include/axp/detail/conversion.hpp:83-95). */
+int axp_sm100_gemm_fp8_blockscaled_swiglu_quant(const void* X, const void* Wg, const void* Wu, const float* sX, const float* sWg,
+                                                const float* sWu, void* Hq, float* Hq_scales, int64_t M, int64_t N, int64_t K,
+                                                int64_t ldx, int64_t ldwg, int64_t ldwu, int64_t ldq, int64_t n_begin, int64_t n_end,
+                                                void* stream, uint32_t* status_dev);
+
 /* Flash-attention forward, bf16, per-row online softmax.
  * Q [B,Hq,S,D], K,V [B,Hkv,S,D], O [B,Hq,S,D] bf16 contiguous; LSE [B,Hq,S] fp32
  * (may be NULL).  s = scale * q.k, optional causal mask (key <= query), kv head =

@@ -31,6 +31,7 @@ EXPORTS = (
     "axp_sm100_gemm_fp8_blockscaled_bias_act",
     "axp_sm100_gemm_bf16_swiglu",
     "axp_sm100_gemm_fp8_blockscaled_swiglu",
+    "axp_sm100_gemm_fp8_blockscaled_swiglu_quant",
     "axp_sm100_gemm_bf16_lincomb",
     "axp_sm100_gemm_fp8_blockscaled_lincomb",
     "axp_sm100_quantize_rows_e4m3",
@@ -126,6 +127,8 @@ def lib() -> ctypes.CDLL:
         L.axp_sm100_gemm_bf16_swiglu.restype = ctypes.c_int
         L.axp_sm100_gemm_fp8_blockscaled_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64, vp, u32p]
         L.axp_sm100_gemm_fp8_blockscaled_swiglu.restype = ctypes.c_int
+        L.axp_sm100_gemm_fp8_blockscaled_swiglu_quant.argtypes = [vp, vp, vp, vp, vp, vp, vp, fp, i64, i64, i64, i64, i64, i64, i64, i64, i64, vp, u32p]
+        L.axp_sm100_gemm_fp8_blockscaled_swiglu_quant.restype = ctypes.c_int
         L.axp_sm100_attn_fwd_bf16.argtypes = [vp, vp, vp, vp, fp, i64, i64, i64, i64, i64, ctypes.c_float,
                                               ctypes.c_int, i64, i64, vp, u32p]
         L.axp_sm100_attn_fwd_bf16.restype = ctypes.c_int

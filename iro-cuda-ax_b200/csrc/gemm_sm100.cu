@@ -81,6 +81,12 @@ struct GemmParams {
     float beta;
     long long ldc;
     uint32_t* status;
+    // gated FP8 with a quantising epilogue: H leaves as E4M3 bytes plus one fp32 scale per row and 128 output columns
+    // (the A operand and 1x128 scales of the next block-scaled GEMM) instead of bf16; null = bf16 output
+    uint8_t* q_out;       // already offset to column n_begin
+    float* q_scales;      // already offset to scale block n_begin / 128
+    long long ldq;
+    int q_scale_ld;       // scale blocks per row of the full output (N / 128)
 #if defined(AXP_SM100_LATENCY_PROBES)
     unsigned long long* debug;   // timestamp buffer of the latency experiments
     int experiment;       // bit 0: skip the promotion arithmetic, bit 1: skip the tensor-memory reads (results invalid; times only)
@@ -100,9 +106,14 @@ struct Pipe {
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t amax_ready;          // quantising epilogue: both warpgroups have published their half-block maxima
+    float amax_half[2][2][kBM];   // [tile parity][warpgroup][row]
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
+
+// Smallest block scale of the quantising epilogue, as in the stand-alone quantiser: the smallest normal float.
+constexpr float kMinBlockScale = 1.17549435e-38f;
 
 __device__ __forceinline__ void report(const GemmParams& p, Pipe* pipe, uint32_t code) {
     *reinterpret_cast<volatile uint32_t*>(&pipe->abort_flag) = 1u;
@@ -205,6 +216,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             rz::BarrierInit::execute(&pipe.tmem_full[a], 1);
             rz::BarrierInit::execute(&pipe.tmem_empty[a], kEpilogueWarps * kCtaGroup);
         }
+        rz::BarrierInit::execute(&pipe.amax_ready, kEpilogueWarps);
         pipe.abort_flag = 0;
         rz::BarrierInitFence::execute();
     }
@@ -355,6 +367,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t acc_phase = 0;
         bool ok = true;
         int n_dbg = 0;
+        int tile_count = 0;      // tiles this CTA has finished (quantising epilogue: parity of the exchange)
         // the accumulator stage goes back to the leader's MMA issuer
         auto release_acc = [&](uint64_t* bar) {
             // the hand-over publishes no generic-proxy memory (the tensor-memory reads have completed), so the remote
@@ -437,7 +450,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
                 }
                 if constexpr (kGated) {
-                    if (ok && row_ok) {
+                    if (p.q_out != nullptr) {
+                        // Quantising epilogue: the bf16 values this kernel would have stored are quantised in registers exactly
+                        // as the stand-alone quantiser would quantise them (block maximum / 448, IEEE divisions, saturating
+                        // E4M3 conversion).  The 128-column scale block of a row is this tile's whole output row: its two
+                        // halves belong to the row's threads in the two warpgroups, which exchange their maxima through
+                        // shared memory behind an mbarrier (bounded wait, like every other wait of the kernel).
+                        if (!ok) break;
+                        uint32_t hw[kCols / 4];
+                        float amax = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < kCols / 4; ++i) {
+                            hw[i] = rz::BiasActFma::gated(accum[2 * i], accum[2 * i + 1], accum[kCols / 2 + 2 * i], accum[kCols / 2 + 2 * i + 1]);
+                            if (ocol0 + 2 * i < p.N)
+                                amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(hw[i] << 16)), fabsf(__uint_as_float(hw[i] & 0xffff0000u))));
+                        }
+                        const int par = tile_count & 1;
+                        pipe.amax_half[par][g][row_in_tile] = amax;
+                        __syncwarp();
+                        if (lane == 0) rz::BarrierArrive::execute(&pipe.amax_ready);
+                        if (!rz::BarrierWait::execute(&pipe.amax_ready, uint32_t(tile_count & 1), abort_flag)) {
+                            if (lane == 0) report(p, &pipe, rz::kRoleEpilogue | rz::kBarOther);
+                            ok = false;
+                            break;
+                        }
+                        amax = fmaxf(amax, pipe.amax_half[par][g ^ 1][row_in_tile]);
+                        const float scale = amax > 0.0f ? fmaxf(__fdiv_rn(amax, 448.0f), kMinBlockScale) : 1.0f;
+                        const float inv = __fdiv_rn(1.0f, scale);
+                        if (row_ok && ocol0 < p.N) {
+                            uint8_t* qrow = p.q_out + (long long)row * p.ldq + ocol0;
+#pragma unroll
+                            for (int c = 0; c < kCols / 32; ++c) {      // 16 outputs = 16 bytes per store
+                                uint32_t q[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const uint32_t w0 = hw[c * 8 + 2 * i], w1 = hw[c * 8 + 2 * i + 1];
+                                    q[i] = rz::PackE4m3x4::execute(__uint_as_float(w0 << 16) * inv, __uint_as_float(w0 & 0xffff0000u) * inv,
+                                                                   __uint_as_float(w1 << 16) * inv, __uint_as_float(w1 & 0xffff0000u) * inv);
+                                }
+                                *reinterpret_cast<uint4*>(qrow + c * 16) = make_uint4(q[0], q[1], q[2], q[3]);
+                            }
+                            if (g == 0) p.q_scales[(long long)row * p.q_scale_ld + tn] = scale;
+                        }
+                        ++tile_count;
+                    } else if (ok && row_ok) {
                         __nv_bfloat16* orow = p.C + (long long)row * p.ldc + ocol0;
 #pragma unroll
                         for (int c = 0; c < kCols / 16; ++c) {
@@ -956,11 +1012,15 @@ int launch_gated(const void* X, const void* Wg, const void* Wu, void* H, int64_t
 }
 
 // E4M3 block-scaled operands: X [M,K] with 1x128 scales sX, Wg / Wu [N,K] with 128x128 scales sWg / sWu
+// `Hq_scales` non-null: the quantising epilogue - H is then E4M3 bytes [M,N] (ldh in bytes = elements) and Hq_scales
+// [M, N/128] fp32, the operand pair of the next block-scaled GEMM
 int launch_gated_fp8(const void* X, const void* Wg, const void* Wu, const float* sX, const float* sWg, const float* sWu, void* H, int64_t M,
                      int64_t N, int64_t K, int64_t ldx, int64_t ldwg, int64_t ldwu, int64_t ldh, int64_t n_begin, int64_t n_end, void* stream,
-                     uint32_t* status_dev) {
+                     uint32_t* status_dev, float* Hq_scales = nullptr) {
     using namespace axp_shim;
     if (!X || !Wg || !Wu || !H || !sX || !sWg || !sWu) return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu: null pointer argument");
+    if (Hq_scales && (N % 128 != 0 || (n_end - n_begin) % 128 != 0 || ldh % 16 != 0))
+        return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu, quantised output: N and the column range must be multiples of the 128-wide scale block, ldq of 16");
     if (M <= 0 || N <= 0 || K <= 0) return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu: M, N, K must be positive");
     if (n_begin < 0 || n_end > N || n_begin > n_end)
         return fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu: column range [%lld,%lld) outside [0,%lld)", (long long)n_begin, (long long)n_end, (long long)N);
@@ -1006,6 +1066,13 @@ int launch_gated_fp8(const void* X, const void* Wg, const void* Wu, const float*
     p.alpha = 1.0f;
     p.ldc = ldh;
     p.status = status_dev;
+    if (Hq_scales) {
+        p.C = nullptr;
+        p.q_out = static_cast<uint8_t*>(H) + n_begin;
+        p.q_scales = Hq_scales + n_begin / 128;
+        p.ldq = ldh;
+        p.q_scale_ld = int(N / 128);
+    }
     // Single CTAs by default: with two scale streams per K block the pair form (the leader stages the gate rows, its peer
     // the up rows; option "gemm.cta_group" = 2) measured slower here (1681 against 1826 TFLOP/s on the MLP gate / up shape),
     // unlike the plain block-scaled kernel.
@@ -1048,6 +1115,15 @@ extern "C" int axp_sm100_gemm_fp8_blockscaled_swiglu(const void* X, const void* 
                                                      void* stream, uint32_t* status_dev) {
     axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_fp8_blockscaled_swiglu");
     return launch_gated_fp8(X, Wg, Wu, sX, sWg, sWu, H, M, N, K, ldx, ldwg, ldwu, ldh, n_begin, n_end, stream, status_dev);
+}
+
+extern "C" int axp_sm100_gemm_fp8_blockscaled_swiglu_quant(const void* X, const void* Wg, const void* Wu, const float* sX, const float* sWg,
+                                                           const float* sWu, void* Hq, float* Hq_scales, int64_t M, int64_t N, int64_t K,
+                                                           int64_t ldx, int64_t ldwg, int64_t ldwu, int64_t ldq, int64_t n_begin,
+                                                           int64_t n_end, void* stream, uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_fp8_blockscaled_swiglu_quant");
+    if (!Hq_scales) return axp_shim::fail(AXP_ERR_BAD_ARG, "gemm fp8 swiglu, quantised output: scales pointer is null");
+    return launch_gated_fp8(X, Wg, Wu, sX, sWg, sWu, Hq, M, N, K, ldx, ldwg, ldwu, ldq, n_begin, n_end, stream, status_dev, Hq_scales);
 }
 
 extern "C" int axp_sm100_gemm_bf16_swiglu(const void* X, const void* Wg, const void* Wu, void* H, int64_t M, int64_t N,

@@ -186,6 +186,37 @@ def gemm_fp8_blockscaled_swiglu(X, Wg, Wu, sX, sWg, sWu, out=None, n_range=None)
     return out
 
 
+def gemm_fp8_blockscaled_swiglu_quant(X, Wg, Wu, sX, sWg, sWu, out=None, scales=None, n_range=None):
+    """The gate / up pass with a quantising epilogue: returns (Hq [M,N] float8_e4m3fn, scales [M,N/128] f32), bit for bit
+    ``quantize_rows_e4m3(gemm_fp8_blockscaled_swiglu(...))`` without the bf16 H ever reaching HBM: the A / sA operands of
+    the down projection.  N and the column range must be multiples of 128."""
+    _need_cuda(X, Wg, Wu, sX, sWg, sWu, out, scales)
+    for t in (X, Wg, Wu):
+        if t.dtype not in (torch.float8_e4m3fn, torch.uint8):
+            raise TypeError("X, Wg, Wu must be float8_e4m3fn (or uint8 bytes)")
+    M, K = X.shape
+    N = Wg.shape[0]
+    if Wg.shape != Wu.shape or Wg.shape[1] != K or X.stride(1) != 1 or Wg.stride(1) != 1 or Wu.stride(1) != 1:
+        raise ValueError("X [M,K], Wg and Wu [N,K] must be K-contiguous with equal shapes")
+    kb, nb = K // 128, (N + 127) // 128
+    for s_, shape in ((sX, (M, kb)), (sWg, (nb, kb)), (sWu, (nb, kb))):
+        if s_.dtype != torch.float32 or tuple(s_.shape) != shape or not s_.is_contiguous():
+            raise ValueError(f"scales must be contiguous float32 of shape {shape}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=X.device)
+    if scales is None:
+        scales = torch.empty((M, N // 128), dtype=torch.float32, device=X.device)
+    if out.dtype not in (torch.float8_e4m3fn, torch.uint8) or out.stride(1) != 1 or tuple(out.shape) != (M, N):
+        raise ValueError("out must be an [M,N] E4M3 (or uint8) matrix with contiguous rows")
+    if scales.dtype != torch.float32 or tuple(scales.shape) != (M, N // 128) or not scales.is_contiguous():
+        raise ValueError("scales must be contiguous float32 [M, N/128]")
+    n0, n1 = n_range if n_range is not None else (0, N)
+    capi.check(capi.lib().axp_sm100_gemm_fp8_blockscaled_swiglu_quant(
+        _ptr(X), _ptr(Wg), _ptr(Wu), _ptr(sX), _ptr(sWg), _ptr(sWu), _ptr(out), _ptr(scales), M, N, K, X.stride(0), Wg.stride(0),
+        Wu.stride(0), out.stride(0), n0, n1, _stream(), _ptr(status_word(X.device))))
+    return out, scales
+
+
 def quantize_rows_e4m3(X, out=None, scales=None):
     """bf16 X [M,K] -> (Q [M,K] float8_e4m3fn, scales [M,K/128] f32): the A / sA operands of the FP8 GEMM."""
     _need_cuda(X, out, scales)

@@ -330,6 +330,50 @@ def test_fp8_swiglu_cta_pair_option_reproduces_the_default(pkg, dev):
         assert torch.equal(H1.view(torch.int16), H2.view(torch.int16))
 
 
+@pytest.mark.parametrize("cta_group", [0, 2])
+def test_fp8_swiglu_quantising_epilogue_equals_gemm_then_quantiser(pkg, oracle, dev, cta_group):
+    """The gate / up pass with the quantising epilogue leaves, bit for bit, what the stand-alone quantiser makes of the bf16
+    result of the plain gate / up pass (codes and 1x128 scales), on full tiles, ragged M, several K blocks and a column
+    shard; against the CPU oracle chain within the block-scaled GEMM's tolerance after dequantisation."""
+    pkg.capi.set_option("gemm.cta_group", cta_group)
+    try:
+        for (M, N, K, n_range) in ((256, 256, 512, None), (200, 384, 256, None), (384, 1024, 384, (128, 640)), (1, 128, 128, None),
+                                   (130, 640, 1024, None)):
+            X, Wg, sX, sWg = pkg.synth.fp8_gemm_inputs(M, N, K, seed=81)
+            _, Wu, _, sWu = pkg.synth.fp8_gemm_inputs(M, N, K, seed=82)
+            d = [t.to(dev) for t in (X, Wg, Wu, sX * 0.0625, sWg, sWu)]
+            H = pkg.ops.gemm_fp8_blockscaled_swiglu(*d)
+            Qw, Sw = pkg.ops.quantize_rows_e4m3(H)
+            Q = torch.full((M, N), 0x7f, dtype=torch.uint8, device=dev)
+            S = torch.full((M, N // 128), float("nan"), dtype=torch.float32, device=dev)
+            pkg.ops.gemm_fp8_blockscaled_swiglu_quant(*d, out=Q, scales=S, n_range=n_range)
+            pkg.ops.check_status(dev)
+            n0, n1 = n_range or (0, N)
+            assert torch.equal(Q[:, n0:n1], Qw.view(torch.uint8)[:, n0:n1])
+            assert torch.equal(S[:, n0 // 128:n1 // 128].view(torch.int32), Sw[:, n0 // 128:n1 // 128].view(torch.int32))
+            if n_range:        # nothing outside the shard is touched
+                assert (Q[:, :n0] == 0x7f).all() and (Q[:, n1:] == 0x7f).all()
+                assert torch.isnan(S[:, :n0 // 128]).all() and torch.isnan(S[:, n1 // 128:]).all()
+            # the oracle chain: block-scaled gate / up, then the quantiser (the GPU GEMM is not bit-exact, so dequantised values are compared)
+            Hw = oracle.gemm_fp8_blockscaled_swiglu(u8(X), u8(Wg), u8(Wu), (sX * 0.0625).numpy(), sWg.numpy(), sWu.numpy())
+            want = oracle.bf16_decode(Hw)[:, n0:n1]
+            got = oracle.e4m3_decode(Q.cpu().numpy())[:, n0:n1] * np.repeat(S.cpu().numpy()[:, n0 // 128:n1 // 128], 128, axis=1)
+            assert rel_fro(got, want) <= 4e-2          # E4M3 rounding of the outputs (2^-4 relative) on top of the GEMM's tolerance
+    finally:
+        pkg.capi.set_option("gemm.cta_group", 0)
+
+
+def test_fp8_swiglu_quantising_epilogue_argument_errors(pkg, dev):
+    X, Wg, sX, sWg = pkg.synth.fp8_gemm_inputs(128, 256, 128, seed=1)
+    d = [t.to(dev) for t in (X, Wg, Wg, sX, sWg, sWg)]
+    with pytest.raises(pkg.capi.AxpError) as e:
+        pkg.ops.gemm_fp8_blockscaled_swiglu_quant(*d, n_range=(0, 64))                     # not whole 128-column blocks
+    assert e.value.code == pkg.capi.AXP_ERR_BAD_ARG
+    X2, W2, sX2, sW2 = pkg.synth.fp8_gemm_inputs(128, 192, 128, seed=1)                  # N not a multiple of 128
+    with pytest.raises((pkg.capi.AxpError, ValueError)):
+        pkg.ops.gemm_fp8_blockscaled_swiglu_quant(*[t.to(dev) for t in (X2, W2, W2, sX2, sW2, sW2)])
+
+
 def test_fp8_swiglu_equals_two_gemms_and_elementwise(pkg, oracle, dev):
     """Property at MLP size: the fused pass agrees with SiLU(G) * U from two plain block-scaled GEMM launches (which
     round G and U to bf16 first, hence the tolerance); sampled rows agree with the oracle; a column-sharded run
