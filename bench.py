@@ -16,7 +16,8 @@ The default run also times, in the same process, the other workloads of the metr
 of at least two seconds ("sustained") and one library E4M3 GEMM as a reference point ("library_reference").
 
 Other workloads (--workload): gemm_fp8_strong, gemm_bf16_gate_up, gemm_bf16_down, gemm_bf16_swiglu, gemm_fp8_swiglu,
-gemm_fp8_swiglu_quant (quantising epilogue) / gemm_fp8_swiglu_then_quant (the same result from two kernels),
+gemm_fp8_swiglu_quant (quantising epilogue) / gemm_fp8_swiglu_then_quant (the same result from two kernels), mlp_fp8 (RMSNorm +
+quantiser, gate / up, down: one MLP block in three launches),
 attn_bf16, attn_fp8, quantize_fp8, rmsnorm_quantize_fp8, attn_decode_bf16, attn_decode_fp8; attn_ring / attn_ring_zigzag (two or more GPUs:
 ring attention over one sequence sharded by position, device timing only).
 
@@ -317,6 +318,41 @@ class GemmFp8SwiGLUQuant(GemmFp8SwiGLU):
     def e2e_spec(self):
         s, (Q, S) = self.sets[0], self.q[0]
         return (lambda i, o: self.pkg.ops.gemm_fp8_blockscaled_swiglu_quant(*i, out=o[0], scales=o[1])), list(s[:6]), [Q, S]
+
+
+class MlpFp8(Workload):
+    """One Llama-3-8B MLP block at 16384 tokens on E4M3 block-scaled weights: RMSNorm + quantiser, gate / up GEMM with the
+    quantising epilogue, down GEMM - three launches, no bf16 intermediate in HBM.  Flops: the three projections."""
+    dtype = "e4m3"
+    M, K, N = 16384, 4096, 14336
+    launches_per_step = 3
+    no_host_arms = "a chain of three launches on device-resident weights: device timing only"
+
+    def __init__(self, pkg, dev, rank, world, sets=2):
+        import torch
+
+        super().__init__(pkg, dev, rank, world)
+        M, K, N = self.M, self.K, self.N
+        self.name = f"FP8 MLP block: RMSNorm+quantise -> gate/up (SwiGLU, quantising epilogue) -> down, M={M} hidden={K} intermediate={N} per GPU"
+        self.flops = 3 * 2.0 * M * N * K
+        self.bytes_min = 2 * M * K * 2 + 3 * N * K
+        _, Wg, _, sWg = pkg.synth.fp8_gemm_inputs(8, N, K, seed=5000 + rank, device=dev)
+        _, Wu, _, sWu = pkg.synth.fp8_gemm_inputs(8, N, K, seed=5100 + rank, device=dev)
+        _, Wd, _, sWd = pkg.synth.fp8_gemm_inputs(8, K, N, seed=5200 + rank, device=dev)
+        self.w = (Wg, Wu, Wd, sWg * 0.05, sWu * 0.05, sWd * 0.05)
+        g = torch.Generator(device=dev).manual_seed(77 + rank)
+        self.wn = (1.0 + 0.1 * torch.randn(K, generator=g, device=dev)).to(torch.bfloat16)
+        self.sets = []
+        for s in range(sets):
+            X = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+            ws = (torch.empty((M, K), dtype=torch.float8_e4m3fn, device=dev), torch.empty((M, K // 128), dtype=torch.float32, device=dev),
+                  torch.empty((M, N), dtype=torch.float8_e4m3fn, device=dev), torch.empty((M, N // 128), dtype=torch.float32, device=dev))
+            self.sets.append((X, ws, torch.empty((M, K), dtype=torch.bfloat16, device=dev)))
+
+    def step(self, i):
+        X, ws, Y = self.sets[i % len(self.sets)]
+        Wg, Wu, Wd, sWg, sWu, sWd = self.w
+        self.pkg.ops.mlp_fp8_forward(X, self.wn, Wg, Wu, Wd, sWg, sWu, sWd, out=Y, workspace=ws)
 
 
 class AttnBf16(Workload):
@@ -657,6 +693,8 @@ def make_workload(name, pkg, dev, rank, world):
         return GemmBf16SwiGLU(pkg, dev, rank, world)
     if name == "gemm_fp8_swiglu":
         return GemmFp8SwiGLU(pkg, dev, rank, world)
+    if name == "mlp_fp8":
+        return MlpFp8(pkg, dev, rank, world)
     if name in ("gemm_fp8_swiglu_quant", "gemm_fp8_swiglu_then_quant"):
         return GemmFp8SwiGLUQuant(pkg, dev, rank, world, fused=(name == "gemm_fp8_swiglu_quant"))
     if name == "attn_decode_fp8":
@@ -1009,7 +1047,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="gemm_fp8",
-                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "gemm_fp8_swiglu_quant", "gemm_fp8_swiglu_then_quant", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8", "attn_ring", "attn_ring_zigzag"])
+                    choices=["gemm_fp8", "gemm_fp8_strong", "gemm_bf16_gate_up", "gemm_bf16_down", "gemm_bf16_swiglu", "gemm_fp8_swiglu", "gemm_fp8_swiglu_quant", "gemm_fp8_swiglu_then_quant", "mlp_fp8", "attn_bf16", "attn_fp8", "quantize_fp8", "rmsnorm_quantize_fp8", "attn_decode_bf16", "attn_decode_fp8", "attn_ring", "attn_ring_zigzag"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -1061,7 +1099,8 @@ def main():
     # ---- end to end: host buffers in, host result out, every step ------------------
     if getattr(wl, "no_host_arms", None):
         line["e2e_note"] = wl.no_host_arms
-        line["ring"] = {"kv_bytes_sent_per_gpu_per_call": wl.kv_bytes_per_step, "passes_on_this_rank": wl.launches_per_step - 1}
+        if hasattr(wl, "kv_bytes_per_step"):
+            line["ring"] = {"kv_bytes_sent_per_gpu_per_call": wl.kv_bytes_per_step, "passes_on_this_rank": wl.launches_per_step - 1}
     elif not args.no_e2e:
         line["e2e"] = e2e_record(ctx, wl, max(4, min(args.steps, 24)))
 

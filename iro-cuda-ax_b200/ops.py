@@ -250,6 +250,24 @@ def rmsnorm_quantize_rows_e4m3(X, W, eps: float = 1e-5, out=None, scales=None):
     return out, scales
 
 
+def mlp_fp8_forward(X, w_norm, Wg, Wu, Wd, sWg, sWu, sWd, eps: float = 1e-5, out=None, workspace=None):
+    """One gated MLP block on E4M3 block-scaled weights, three launches and no bf16 intermediate in HBM:
+    ``Y = (SiLU(n . Wg^T) * (n . Wu^T)) . Wd^T`` with ``n = RMSNorm(X) * w_norm``.
+
+    X [M,K] bf16; w_norm [K] bf16; Wg, Wu [N,K] and Wd [K,N] E4M3 with 128x128 scales sWg, sWu [N/128,K/128], sWd [K/128,N/128].
+    RMSNorm + quantiser -> gate / up GEMM with the quantising epilogue -> down GEMM (bf16 out).  ``workspace`` may hold
+    the four intermediates ``(Xq, sX, Hq, sH)`` to avoid allocations.  Returns Y [M,K] bf16."""
+    M, K = X.shape
+    N = Wg.shape[0]
+    if tuple(Wd.shape) != (K, N):
+        raise ValueError("Wd must be [K, N] (rows = output features of the block)")
+    if workspace is None:
+        workspace = (None, None, None, None)
+    Xq, sX = rmsnorm_quantize_rows_e4m3(X, w_norm, eps, out=workspace[0], scales=workspace[1])
+    Hq, sH = gemm_fp8_blockscaled_swiglu_quant(Xq, Wg, Wu, sX, sWg, sWu, out=workspace[2], scales=workspace[3])
+    return gemm_fp8_blockscaled(Hq, Wd, sH, sWd, out=out)
+
+
 def _attn_dims(Q, K, V):
     B, Hq, S, D = Q.shape
     Bk, Hkv, Sk, Dk = K.shape

@@ -374,6 +374,29 @@ def test_fp8_swiglu_quantising_epilogue_argument_errors(pkg, dev):
         pkg.ops.gemm_fp8_blockscaled_swiglu_quant(*[t.to(dev) for t in (X2, W2, W2, sX2, sW2, sW2)])
 
 
+def test_fp8_mlp_block_against_the_oracle_chain(pkg, oracle, dev):
+    """RMSNorm + quantiser -> E4M3 gate / up with the quantising epilogue -> E4M3 down projection, against the same chain of
+    oracle functions.  The first stage is bit-exact; after it the GPU GEMMs differ from the oracle in the last bits, which
+    can move single E4M3 codes of H, so the block's output is compared in the Frobenius norm."""
+    M, K, N = 200, 512, 1024
+    g = torch.Generator().manual_seed(5)
+    X = (torch.randn(M, K, generator=g) * 2.0).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16)
+    _, Wg, _, sWg = pkg.synth.fp8_gemm_inputs(8, N, K, seed=91)
+    _, Wu, _, sWu = pkg.synth.fp8_gemm_inputs(8, N, K, seed=92)
+    _, Wd, _, sWd = pkg.synth.fp8_gemm_inputs(8, K, N, seed=93)
+    sWg, sWu, sWd = sWg * 0.05, sWu * 0.05, sWd * 0.05
+    Y = pkg.ops.mlp_fp8_forward(*(t.to(dev) for t in (X, w, Wg, Wu, Wd, sWg, sWu, sWd)))
+    pkg.ops.check_status(dev)
+    xq, sx = oracle.rmsnorm_quantize_rows_e4m3(u16(X), u16(w), 1e-5)
+    h = oracle.gemm_fp8_blockscaled_swiglu(xq, u8(Wg), u8(Wu), sx, sWg.numpy(), sWu.numpy())
+    hq, sh = oracle.quantize_rows_e4m3(h)
+    want = oracle.bf16_decode(oracle.gemm_fp8_blockscaled(hq, u8(Wd), sh, sWd.numpy()))
+    got = Y.float().cpu().numpy()
+    assert np.isfinite(got).all() and got.shape == (M, K)
+    assert rel_fro(got, want) <= 2e-2
+
+
 def test_fp8_swiglu_equals_two_gemms_and_elementwise(pkg, oracle, dev):
     """Property at MLP size: the fused pass agrees with SiLU(G) * U from two plain block-scaled GEMM launches (which
     round G and U to bf16 first, hence the tolerance); sampled rows agree with the oracle; a column-sharded run
