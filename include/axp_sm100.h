@@ -138,6 +138,16 @@ int axp_sm100_gemm_fp8_blockscaled_swiglu(const void* X, const void* Wg, const v
                                           int64_t ldwu, int64_t ldh, int64_t n_begin, int64_t n_end, void* stream,
                                           uint32_t* status_dev);
 
+/* The block-scaled GEMM (optionally with the bias / activation epilogue) with a quantising epilogue: instead of bf16 C it
+ * leaves Cq [M,N] E4M3 bytes (ldq bytes per row, a multiple of 16) and Cq_scales [M, N/128] fp32, bit for bit what
+ * axp_sm100_quantize_rows_e4m3 produces from the bf16 C of axp_sm100_gemm_fp8_blockscaled(_bias_act): an epilogue thread
+ * owns one 128-column scale block of its row.  bias may be null (act is then ignored).  Requires N % 128 == 0 and a
+ * column range of whole 128-column blocks.  Realizes the reference's CastTile with the fp8_saturate policy
+ * (include/axp/protocol/convert/contracts.hpp:31, include/axp/detail/conversion.hpp:83-95) behind the GEMM recipe. */
+int axp_sm100_gemm_fp8_blockscaled_quant(const void* A, const void* B, const float* sA, const float* sB, const float* bias, int act,
+                                         void* Cq, float* Cq_scales, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                         int64_t ldq, int64_t n_begin, int64_t n_end, void* stream, uint32_t* status_dev);
+
 /* The same pass with a quantising epilogue: instead of bf16 H it leaves Hq [M,N] E4M3 bytes (leading dimension ldq
  * bytes, a multiple of 16) and Hq_scales [M, N/128] fp32 - the A operand and the 1x128 scales of the next block-scaled
  * GEMM (the MLP's down projection) - bit for bit what axp_sm100_quantize_rows_e4m3 produces from the bf16 H of the

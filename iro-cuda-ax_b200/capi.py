@@ -32,6 +32,7 @@ EXPORTS = (
     "axp_sm100_gemm_bf16_swiglu",
     "axp_sm100_gemm_fp8_blockscaled_swiglu",
     "axp_sm100_gemm_fp8_blockscaled_swiglu_quant",
+    "axp_sm100_gemm_fp8_blockscaled_quant",
     "axp_sm100_gemm_bf16_lincomb",
     "axp_sm100_gemm_fp8_blockscaled_lincomb",
     "axp_sm100_quantize_rows_e4m3",
@@ -129,6 +130,8 @@ def lib() -> ctypes.CDLL:
         L.axp_sm100_gemm_fp8_blockscaled_swiglu.restype = ctypes.c_int
         L.axp_sm100_gemm_fp8_blockscaled_swiglu_quant.argtypes = [vp, vp, vp, vp, vp, vp, vp, fp, i64, i64, i64, i64, i64, i64, i64, i64, i64, vp, u32p]
         L.axp_sm100_gemm_fp8_blockscaled_swiglu_quant.restype = ctypes.c_int
+        L.axp_sm100_gemm_fp8_blockscaled_quant.argtypes = [vp, vp, fp, fp, fp, ctypes.c_int, vp, fp, i64, i64, i64, i64, i64, i64, i64, i64, vp, u32p]
+        L.axp_sm100_gemm_fp8_blockscaled_quant.restype = ctypes.c_int
         L.axp_sm100_attn_fwd_bf16.argtypes = [vp, vp, vp, vp, fp, i64, i64, i64, i64, i64, ctypes.c_float,
                                               ctypes.c_int, i64, i64, vp, u32p]
         L.axp_sm100_attn_fwd_bf16.restype = ctypes.c_int

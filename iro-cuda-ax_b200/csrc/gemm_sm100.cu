@@ -510,15 +510,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         }
                     }
                 } else if (ok && row_ok) {
+                    bool stored = false;
+                    if constexpr (kCols == 128) {
+                        if (p.q_out != nullptr) {
+                            // Quantising epilogue: a thread's 128 columns are one scale block of its row.  The bf16 values the
+                            // plain epilogue would store (bias, activation, linear combination included) are quantised in
+                            // registers exactly as the stand-alone quantiser would quantise them.
+                            stored = true;
+                            uint4 w[kCols / 8];
+                            float amax = 0.0f;
 #pragma unroll
-                    for (int c = 0; c < kCols / 8; ++c) {
-                        if (col0 + c * 8 < p.N) {
-                            float f[8];
+                            for (int c = 0; c < kCols / 8; ++c) {
+                                float f[8];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) f[i] = accum[c * 8 + i];
-                            rz::RowStoreVec16::execute(crow + c * 8,
-                                rz::BiasActFma::execute(f, p.bias ? p.bias + col0 + c * 8 : nullptr, p.act,
-                                        p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 8 : nullptr, p.alpha, p.beta));
+                                for (int i = 0; i < 8; ++i) f[i] = accum[c * 8 + i];
+                                w[c] = rz::BiasActFma::execute(f, p.bias ? p.bias + col0 + c * 8 : nullptr, p.act,
+                                        p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 8 : nullptr, p.alpha, p.beta);
+                                const uint32_t ww[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(ww[i] << 16)), fabsf(__uint_as_float(ww[i] & 0xffff0000u))));
+                            }
+                            const float scale = amax > 0.0f ? fmaxf(__fdiv_rn(amax, 448.0f), kMinBlockScale) : 1.0f;
+                            const float inv = __fdiv_rn(1.0f, scale);
+                            if (col0 < p.N) {
+                                uint8_t* qrow = p.q_out + (long long)row * p.ldq + col0;
+#pragma unroll
+                                for (int c = 0; c < kCols / 16; ++c) {      // 16 outputs = 16 bytes per store
+                                    const uint32_t ww[8] = {w[2 * c].x, w[2 * c].y, w[2 * c].z, w[2 * c].w, w[2 * c + 1].x, w[2 * c + 1].y, w[2 * c + 1].z, w[2 * c + 1].w};
+                                    uint32_t q[4];
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i)
+                                        q[i] = rz::PackE4m3x4::execute(__uint_as_float(ww[2 * i] << 16) * inv, __uint_as_float(ww[2 * i] & 0xffff0000u) * inv,
+                                                                       __uint_as_float(ww[2 * i + 1] << 16) * inv, __uint_as_float(ww[2 * i + 1] & 0xffff0000u) * inv);
+                                    *reinterpret_cast<uint4*>(qrow + c * 16) = make_uint4(q[0], q[1], q[2], q[3]);
+                                }
+                                p.q_scales[(long long)row * p.q_scale_ld + tn * (kBN / 128) + g] = scale;
+                            }
+                        }
+                    }
+                    if (!stored) {
+#pragma unroll
+                        for (int c = 0; c < kCols / 8; ++c) {
+                            if (col0 + c * 8 < p.N) {
+                                float f[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) f[i] = accum[c * 8 + i];
+                                rz::RowStoreVec16::execute(crow + c * 8,
+                                    rz::BiasActFma::execute(f, p.bias ? p.bias + col0 + c * 8 : nullptr, p.act,
+                                            p.c_in ? p.c_in + (long long)row * p.ldcin + col0 + c * 8 : nullptr, p.alpha, p.beta));
+                            }
                         }
                     }
                 }
@@ -793,9 +834,13 @@ template <bool kFp8>
 int launch_gemm(const void* A, const void* B, const float* sA, const float* sB, const float* bias, int act, void* C,
                 int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t n_begin, int64_t n_end,
                 void* stream, uint32_t* status_dev, const void* c_in = nullptr, int64_t ldcin = 0, float alpha = 1.0f,
-                float beta = 0.0f) {
+                float beta = 0.0f, float* q_scales = nullptr) {
     using namespace axp_shim;
     constexpr int kElem = kFp8 ? 1 : 2;
+    // q_scales non-null (E4M3 block-scaled only): the quantising epilogue - C is then E4M3 bytes [M,N] with ldc bytes per row
+    // and q_scales [M, N/128] fp32
+    if (q_scales && (!kFp8 || N % 128 != 0 || (n_end - n_begin) % 128 != 0 || ldc % 16 != 0))
+        return fail(AXP_ERR_BAD_ARG, "gemm fp8, quantised output: N and the column range must be multiples of the 128-wide scale block, ldq of 16");
     if (c_in && (ldcin < N || ldcin % 8 != 0 || !aligned16(c_in)))
         return fail(AXP_ERR_BAD_ARG, "gemm lincomb: C input needs ldc >= N, a multiple of 8, and a 16-byte aligned base");
     constexpr int kElemsPerRow = kRowBytes / kElem;
@@ -835,7 +880,8 @@ int launch_gemm(const void* A, const void* B, const float* sA, const float* sB, 
     // hand-over the FP8 pair was 45 % slower than single CTAs; with the relaxed arrive it is 3 % faster: 2115 against
     // 2053 TFLOP/s on 8192^3.)
     constexpr cfg::Gemm kDefault = kFp8 ? cfg::kGemmFp8 : cfg::kGemmBf16;
-    const int epi_wg = (epi_wg_opt == 2 || epi_wg_opt == 4) ? epi_wg_opt : kDefault.threads / 128 - 1;
+    // (the quantising epilogue needs a thread to own a whole 128-column scale block: two epilogue warpgroups)
+    const int epi_wg = q_scales ? 2 : (epi_wg_opt == 2 || epi_wg_opt == 4) ? epi_wg_opt : kDefault.threads / 128 - 1;
     const int cta_group = (cta_group_opt == 1 || cta_group_opt == 2) ? cta_group_opt : kDefault.cta_group;
     const int b_box_div = cta_group;      // a CTA of a pair loads half of the tile's B rows
 
@@ -856,7 +902,7 @@ int launch_gemm(const void* A, const void* B, const float* sA, const float* sB, 
         if (int rc = make_tensor_map(&tmB, dt, 2, b_base, dims, strides, box); rc != AXP_OK) return rc;
     }
 
-    GemmParams p;
+    GemmParams p = {};
     p.sA = sA;
     p.sB = sB;
     p.C = static_cast<__nv_bfloat16*>(C) + n_begin;
@@ -873,6 +919,13 @@ int launch_gemm(const void* A, const void* B, const float* sA, const float* sB, 
     p.beta = beta;
     p.ldc = ldc;
     p.status = status_dev;
+    if (q_scales) {
+        p.C = nullptr;
+        p.q_out = static_cast<uint8_t*>(C) + n_begin;
+        p.q_scales = q_scales + n_begin / 128;
+        p.ldq = ldc;
+        p.q_scale_ld = int(N / 128);
+    }
 #if defined(AXP_SM100_LATENCY_PROBES)
     p.debug = reinterpret_cast<unsigned long long*>(axp_shim::debug_pointer().load(std::memory_order_relaxed));
     p.experiment = axp_shim::option_slot(axp_shim::kOptGemmExperiment).load(std::memory_order_relaxed);
@@ -1138,6 +1191,16 @@ extern "C" int axp_sm100_gemm_fp8_blockscaled(const void* A, const void* B, cons
                                               int64_t n_begin, int64_t n_end, void* stream, uint32_t* status_dev) {
     axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_fp8_blockscaled");
     return launch_gemm<true>(A, B, sA, sB, nullptr, AXP_ACT_NONE, C, M, N, K, lda, ldb, ldc, n_begin, n_end, stream, status_dev);
+}
+
+extern "C" int axp_sm100_gemm_fp8_blockscaled_quant(const void* A, const void* B, const float* sA, const float* sB, const float* bias,
+                                                    int act, void* Cq, float* Cq_scales, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                                    int64_t ldb, int64_t ldq, int64_t n_begin, int64_t n_end, void* stream,
+                                                    uint32_t* status_dev) {
+    axp_shim::NvtxRange nvtx_range("axp_sm100_gemm_fp8_blockscaled_quant");
+    if (!Cq_scales) return axp_shim::fail(AXP_ERR_BAD_ARG, "gemm fp8, quantised output: scales pointer is null");
+    return launch_gemm<true>(A, B, sA, sB, bias, act, Cq, M, N, K, lda, ldb, ldq, n_begin, n_end, stream, status_dev, nullptr, 0, 1.0f, 0.0f,
+                             Cq_scales);
 }
 
 extern "C" int axp_sm100_gemm_bf16_lincomb(const void* A, const void* B, const void* Cin, void* D, float alpha, float beta, int64_t M,

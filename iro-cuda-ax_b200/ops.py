@@ -186,6 +186,37 @@ def gemm_fp8_blockscaled_swiglu(X, Wg, Wu, sX, sWg, sWu, out=None, n_range=None)
     return out
 
 
+def gemm_fp8_blockscaled_quant(A, B, sA, sB, out=None, scales=None, n_range=None, bias=None, act: int = capi.AXP_ACT_NONE):
+    """The block-scaled GEMM with a quantising epilogue: returns (Cq [M,N] float8_e4m3fn, scales [M,N/128] f32), bit for bit
+    ``quantize_rows_e4m3(gemm_fp8_blockscaled(...))`` (bias / activation included) without the bf16 C reaching HBM."""
+    _need_cuda(A, B, sA, sB, out, scales, bias)
+    if not (_is_fp8(A) and _is_fp8(B)):
+        raise TypeError("A and B must be float8_e4m3fn (or uint8 bytes)")
+    if sA.dtype != torch.float32 or sB.dtype != torch.float32:
+        raise TypeError("scales must be float32")
+    M, K = A.shape
+    N = B.shape[0]
+    if B.shape[1] != K or A.stride(1) != 1 or B.stride(1) != 1:
+        raise ValueError("A [M,K] and B [N,K] must be K-contiguous")
+    if tuple(sA.shape) != (M, K // 128) or tuple(sB.shape) != ((N + 127) // 128, K // 128) or not (sA.is_contiguous() and sB.is_contiguous()):
+        raise ValueError("sA [M,K/128] and sB [ceil(N/128),K/128] must be contiguous")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=A.device)
+    if scales is None:
+        scales = torch.empty((M, N // 128), dtype=torch.float32, device=A.device)
+    if tuple(out.shape) != (M, N) or out.stride(1) != 1 or not _is_fp8(out):
+        raise ValueError("out must be an [M,N] E4M3 (or uint8) matrix with contiguous rows")
+    if scales.dtype != torch.float32 or tuple(scales.shape) != (M, N // 128) or not scales.is_contiguous():
+        raise ValueError("scales must be contiguous float32 [M, N/128]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous float32 vector of N elements")
+    n0, n1 = n_range if n_range is not None else (0, N)
+    capi.check(capi.lib().axp_sm100_gemm_fp8_blockscaled_quant(
+        _ptr(A), _ptr(B), _ptr(sA), _ptr(sB), _ptr(bias) if bias is not None else None, act, _ptr(out), _ptr(scales), M, N, K, A.stride(0),
+        B.stride(0), out.stride(0), n0, n1, _stream(), _ptr(status_word(A.device))))
+    return out, scales
+
+
 def gemm_fp8_blockscaled_swiglu_quant(X, Wg, Wu, sX, sWg, sWu, out=None, scales=None, n_range=None):
     """The gate / up pass with a quantising epilogue: returns (Hq [M,N] float8_e4m3fn, scales [M,N/128] f32), bit for bit
     ``quantize_rows_e4m3(gemm_fp8_blockscaled_swiglu(...))`` without the bf16 H ever reaching HBM: the A / sA operands of

@@ -374,6 +374,38 @@ def test_fp8_swiglu_quantising_epilogue_argument_errors(pkg, dev):
         pkg.ops.gemm_fp8_blockscaled_swiglu_quant(*[t.to(dev) for t in (X2, W2, W2, sX2, sW2, sW2)])
 
 
+@pytest.mark.parametrize("cta_group", [0, 1])
+def test_fp8_gemm_quantising_epilogue_equals_gemm_then_quantiser(pkg, oracle, dev, cta_group):
+    """The block-scaled GEMM with the quantising epilogue leaves, bit for bit, what the stand-alone quantiser makes of the bf16
+    result (codes and 1x128 scales): plain and with bias + SiLU, ragged M, several K blocks, a column shard."""
+    pkg.capi.set_option("gemm.cta_group", cta_group)
+    try:
+        for (M, N, K, n_range, fused) in ((256, 256, 512, None, False), (200, 384, 256, None, True), (384, 1024, 384, (256, 768), False),
+                                          (1, 128, 128, None, False), (130, 640, 1024, (128, 640), True)):
+            A, B, sA, sB = pkg.synth.fp8_gemm_inputs(M, N, K, seed=95)
+            d = [t.to(dev) for t in (A, B, sA, sB)]
+            bias = (torch.randn(N, generator=torch.Generator().manual_seed(3)) * 4.0).to(dev) if fused else None
+            act = pkg.capi.AXP_ACT_SILU if fused else pkg.capi.AXP_ACT_NONE
+            C = pkg.ops.gemm_fp8_blockscaled(*d, bias=bias, act=act)
+            Qw, Sw = pkg.ops.quantize_rows_e4m3(C)
+            Q = torch.full((M, N), 0x7f, dtype=torch.uint8, device=dev)
+            S = torch.full((M, N // 128), float("nan"), dtype=torch.float32, device=dev)
+            pkg.ops.gemm_fp8_blockscaled_quant(*d, out=Q, scales=S, n_range=n_range, bias=bias, act=act)
+            pkg.ops.check_status(dev)
+            n0, n1 = n_range or (0, N)
+            assert torch.equal(Q[:, n0:n1], Qw.view(torch.uint8)[:, n0:n1])
+            assert torch.equal(S[:, n0 // 128:n1 // 128].view(torch.int32), Sw[:, n0 // 128:n1 // 128].view(torch.int32))
+            if n_range:
+                assert (Q[:, :n0] == 0x7f).all() and (Q[:, n1:] == 0x7f).all()
+                assert torch.isnan(S[:, :n0 // 128]).all() and torch.isnan(S[:, n1 // 128:]).all()
+    finally:
+        pkg.capi.set_option("gemm.cta_group", 0)
+    with pytest.raises(pkg.capi.AxpError) as e:
+        A, B, sA, sB = (t.to(dev) for t in pkg.synth.fp8_gemm_inputs(128, 256, 128, seed=1))
+        pkg.ops.gemm_fp8_blockscaled_quant(A, B, sA, sB, n_range=(0, 192))
+    assert e.value.code == pkg.capi.AXP_ERR_BAD_ARG
+
+
 def test_fp8_mlp_block_against_the_oracle_chain(pkg, oracle, dev):
     """RMSNorm + quantiser -> E4M3 gate / up with the quantising epilogue -> E4M3 down projection, against the same chain of
     oracle functions.  The first stage is bit-exact; after it the GPU GEMMs differ from the oracle in the last bits, which
